@@ -1,0 +1,566 @@
+/*
+ * TEST INFRASTRUCTURE — not part of the shipped library.
+ *
+ * CPU restatement of the five IntentDSL operator kernels the b200 provider
+ * accelerates.  Only the test-suite, the smoke check and the CPU-baseline leg
+ * of the benchmark may load this file; the product path never does.
+ *
+ * PARITY UNPINNED: the reference ships no tests, golden vectors or
+ * known-answer fixtures for these operators, and neither its compiler
+ * (needs the LLVM/MLIR 20 SDK) nor its CPU provider (needs the Mojo
+ * compiler) can run where this was written.  This file therefore follows the
+ * kernel definitions and the documented numerics contract line by line:
+ *
+ *   kernels      python/intent/examples/kernels/normalization/softmax.py:23-66
+ *                python/intent/examples/kernels/normalization/layer_norm.py:9-85
+ *                python/intent/examples/kernels/contraction/gemm.py:54-92
+ *                python/intent/examples/kernels/streaming/attention.py:52-114,
+ *                  :150-236, :417-425, :428-553
+ *                python/intent/examples/kernels/sparse/csr_spmm.py:12-33
+ *   numerics     doc/dsl/types-numerics-and-effects.en.md:69-177
+ *   C spellings  lib/Serialization/Scalar.cpp:271-302   (fmax signed-zero rule,
+ *                  expf, 1.0f/sqrtf)
+ *   approx ops   lib/Conversion/KIRToCPU/Arithmetic.cpp:13-98 (exp2/fdiv + FTZ)
+ *   contraction  lib/Target/Mojo/Transforms/Matrix.cpp:395-413 (exact widening,
+ *                  ascending-K fused multiply-add chain into f32)
+ *   fp env       python/intent/runtime/mojo/fp_environment.c:4-8 (RN, FTZ/DAZ off)
+ *   contraction  python/intent/targets/mojo.py:71-76 (--fp-mode=contract=off)
+ *   task split   python/intent/runtime/mojo/task_dispatch.c:44-49
+ *
+ * Where the contract leaves a choice (reduce may re-associate, region_fold
+ * slices are compiler-chosen) the choice made here is stated at the function.
+ *
+ * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fno-math-errno -pthread
+ * (worker threads are plain pthreads: GNU OpenMP is not installed everywhere this runs;
+ * the per-rank ranges are the ones task_dispatch.c computes)
+ */
+#define _GNU_SOURCE
+#include <math.h>
+#include <pthread.h>
+#include <sched.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+#include <xmmintrin.h>
+
+#define ORACLE_OK 0
+#define ORACLE_BAD_INDEX 1
+#define ORACLE_NO_MEMORY 2
+
+/* ---- floating-point environment: fp_environment.c:4-8 ------------------- */
+static uint32_t enter_ieee(void) {
+  uint32_t previous = _mm_getcsr();
+  _mm_setcsr(previous & ~(UINT32_C(0x8040) | UINT32_C(0x6000)));
+  return previous;
+}
+static void leave_ieee(uint32_t previous) { _mm_setcsr(previous); }
+
+/* ---- static contiguous split: task_dispatch.c:44-49 --------------------- */
+typedef void (*range_task)(void *, int64_t, int64_t);
+
+struct team_member {
+  range_task task; void *captures;
+  int64_t begin, end;
+};
+
+static void *team_entry(void *opaque) {
+  struct team_member *member = opaque;
+  uint32_t csr = enter_ieee();
+  member->task(member->captures, member->begin, member->end);
+  leave_ieee(csr);
+  return NULL;
+}
+
+static void dispatch_team(range_task task, void *captures, int64_t count, int64_t workers) {
+  if (count <= 0) return;
+  if (workers > count) workers = count;
+  if (workers <= 1) {
+    struct team_member self = {task, captures, 0, count};
+    team_entry(&self);
+    return;
+  }
+  if (workers > 1024) workers = 1024;
+  struct team_member members[1024];
+  pthread_t threads[1024];
+  int64_t chunk = count / workers, extra = count % workers;
+  for (int64_t rank = 0; rank < workers; ++rank) {
+    int64_t begin = rank * chunk + (rank < extra ? rank : extra);
+    members[rank] = (struct team_member){task, captures, begin, begin + chunk + (rank < extra)};
+  }
+  int64_t started = 0;
+  for (int64_t rank = 1; rank < workers; ++rank, ++started)
+    if (pthread_create(&threads[rank], NULL, team_entry, &members[rank]) != 0) break;
+  team_entry(&members[0]);
+  /* ranges whose thread could not be created run on the caller */
+  for (int64_t rank = started + 1; rank < workers; ++rank) team_entry(&members[rank]);
+  for (int64_t rank = 1; rank <= started; ++rank) pthread_join(threads[rank], NULL);
+}
+
+/* ---- scalar helpers ----------------------------------------------------- */
+
+/* maximum_num: one-sided NaN ignored; signed-zero tie resolved explicitly
+   (Scalar.cpp:271-283). */
+static inline float maximum_num(float a, float b) {
+  if (a == 0.0f && b == 0.0f) return (signbit(a) && signbit(b)) ? -0.0f : 0.0f;
+  return fmaxf(a, b);
+}
+
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+/* f32 -> bf16, round to nearest even, overflow to infinity, NaN kept NaN
+   (types-numerics-and-effects.en.md:112). */
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+static inline float f16_to_f32(uint16_t h) {
+  _Float16 v;
+  memcpy(&v, &h, 2);
+  return (float)v;
+}
+static inline uint16_t f32_to_f16(float f) {
+  _Float16 v = (_Float16)f; /* RNE, overflow to infinity */
+  uint16_t h;
+  memcpy(&h, &v, 2);
+  return h;
+}
+
+/* Subnormal flush used at the boundary of approximate operations
+   (Arithmetic.cpp:14-21). */
+static inline float flush_f32(float v) { return fabsf(v) < 0x1.0p-126f ? v * 0.0f : v; }
+
+/* exp2(approximate, flush_to_zero): Arithmetic.cpp:80-98. */
+static inline float exp2_approx_ftz(float x) {
+  float r = exp2f(x);
+  return r < 0x1.0p-126f ? 0.0f : r;
+}
+
+/* fdiv(approximate, flush_to_zero): Arithmetic.cpp:59-78. */
+static inline float fdiv_approx_ftz(float a, float b) {
+  a = flush_f32(a);
+  b = flush_f32(b);
+  float quotient = a / b;
+  float limit = a * (b < 0.0f ? -0.0f : 0.0f);
+  float result = fabsf(b) > 0x1.0p126f ? limit : quotient;
+  return flush_f32(result);
+}
+
+/* Reduction order used for every `reduce` below: 16 interleaved lane
+   accumulators (element i goes to lane i%16, ascending i), then the lanes are
+   combined pairwise 8,4,2,1.  `reduce` permits any parenthesisation and
+   permutation (types-numerics-and-effects.en.md:156); this is the shape a
+   16-wide vector unit produces and is fixed so results are reproducible. */
+#define LANES 16
+
+static inline float lanes_sum(float *lane) {
+  for (int width = LANES / 2; width >= 1; width /= 2)
+    for (int i = 0; i < width; ++i) lane[i] = lane[i] + lane[i + width];
+  return lane[0];
+}
+static inline float lanes_max(float *lane) {
+  for (int width = LANES / 2; width >= 1; width /= 2)
+    for (int i = 0; i < width; ++i) lane[i] = maximum_num(lane[i], lane[i + width]);
+  return lane[0];
+}
+
+/* ======================================================================== */
+/* a1  stable_softmax / stable_softmax_f16 / chunked_softmax_bf16            */
+/*     softmax.py:23-66                                                      */
+/* ======================================================================== */
+enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+
+static inline float load_as_f32(const void *base, int64_t index, int dtype) {
+  switch (dtype) {
+  case DT_F32: return ((const float *)base)[index];
+  case DT_F16: return f16_to_f32(((const uint16_t *)base)[index]);
+  default: return bf16_to_f32(((const uint16_t *)base)[index]);
+  }
+}
+static inline void store_from_f32(void *base, int64_t index, int dtype, float v) {
+  switch (dtype) {
+  case DT_F32: ((float *)base)[index] = v; break;
+  case DT_F16: ((uint16_t *)base)[index] = f32_to_f16(v); break;
+  default: ((uint16_t *)base)[index] = f32_to_bf16(v); break;
+  }
+}
+
+struct softmax_args {
+  const void *x; void *y;
+  int64_t n, xs0, xs1, ys0, ys1;
+  int dtype;
+};
+
+static void softmax_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct softmax_args *a = opaque;
+  float *row = malloc(sizeof(float) * (size_t)(a->n > 0 ? a->n : 1));
+  for (int64_t r = begin; r < end; ++r) {
+    float lane[LANES];
+    for (int i = 0; i < LANES; ++i) lane[i] = -INFINITY;
+    for (int64_t c = 0; c < a->n; ++c) {
+      row[c] = load_as_f32(a->x, r * a->xs0 + c * a->xs1, a->dtype);
+      lane[c % LANES] = maximum_num(lane[c % LANES], row[c]);
+    }
+    float maximum = lanes_max(lane);
+    for (int i = 0; i < LANES; ++i) lane[i] = 0.0f;
+    for (int64_t c = 0; c < a->n; ++c) {
+      row[c] = expf(row[c] - maximum);
+      lane[c % LANES] = lane[c % LANES] + row[c];
+    }
+    float denominator = lanes_sum(lane);
+    if (a->dtype == DT_F32) {
+      /* softmax.py:35-36: multiply by the reciprocal */
+      float inverse = 1.0f / denominator;
+      for (int64_t c = 0; c < a->n; ++c)
+        ((float *)a->y)[r * a->ys0 + c * a->ys1] = row[c] * inverse;
+    } else {
+      /* softmax.py:51, :66: true division, then the narrowing cast */
+      for (int64_t c = 0; c < a->n; ++c)
+        store_from_f32(a->y, r * a->ys0 + c * a->ys1, a->dtype, row[c] / denominator);
+    }
+  }
+  free(row);
+}
+
+int oracle_softmax(const void *x, void *y, int64_t m, int64_t n, int64_t xs0, int64_t xs1,
+                   int64_t ys0, int64_t ys1, int dtype, int64_t workers) {
+  struct softmax_args a = {x, y, n, xs0, xs1, ys0, ys1, dtype};
+  dispatch_team(softmax_rows, &a, m, workers);
+  return ORACLE_OK;
+}
+
+/* ======================================================================== */
+/* a2  layer_norm_f16 / layer_norm_bf16 / weighted_layer_norm (f32)          */
+/*     layer_norm.py:9-85                                                    */
+/* ======================================================================== */
+struct layer_norm_args {
+  const void *x, *w, *b; void *y;
+  int64_t n, xs0, xs1, ws0, bs0, ys0, ys1;
+  float inverse_features, epsilon;
+  int dtype;
+};
+
+static void layer_norm_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct layer_norm_args *a = opaque;
+  float *row = malloc(sizeof(float) * (size_t)(a->n > 0 ? a->n : 1));
+  for (int64_t r = begin; r < end; ++r) {
+    float lane[LANES];
+    for (int i = 0; i < LANES; ++i) lane[i] = 0.0f;
+    for (int64_t c = 0; c < a->n; ++c) {
+      row[c] = load_as_f32(a->x, r * a->xs0 + c * a->xs1, a->dtype);
+      lane[c % LANES] = lane[c % LANES] + row[c];
+    }
+    float mean = lanes_sum(lane) * a->inverse_features;
+    float variance;
+    for (int i = 0; i < LANES; ++i) lane[i] = 0.0f;
+    if (a->dtype == DT_F32) {
+      /* weighted_layer_norm, layer_norm.py:21-28: uncentred second moment */
+      for (int64_t c = 0; c < a->n; ++c) lane[c % LANES] = lane[c % LANES] + row[c] * row[c];
+      float second_moment = lanes_sum(lane) * a->inverse_features;
+      variance = second_moment - mean * mean;
+      for (int64_t c = 0; c < a->n; ++c) row[c] = row[c] - mean;
+    } else {
+      /* layer_norm_f16 / _bf16, layer_norm.py:45-50: centred two-pass variance */
+      for (int64_t c = 0; c < a->n; ++c) {
+        row[c] = row[c] - mean;
+        lane[c % LANES] = lane[c % LANES] + row[c] * row[c];
+      }
+      variance = lanes_sum(lane) * a->inverse_features;
+    }
+    float scale = 1.0f / sqrtf(variance + a->epsilon); /* Scalar.cpp:293-295 */
+    for (int64_t c = 0; c < a->n; ++c) {
+      float weight = load_as_f32(a->w, c * a->ws0, a->dtype);
+      float bias = load_as_f32(a->b, c * a->bs0, a->dtype);
+      /* left-to-right, no fused multiply-add (contract=off on the CPU provider) */
+      float value = row[c] * scale * weight + bias;
+      store_from_f32(a->y, r * a->ys0 + c * a->ys1, a->dtype, value);
+    }
+  }
+  free(row);
+}
+
+int oracle_layer_norm(const void *x, const void *w, const void *b, void *y, int64_t m, int64_t n,
+                      int64_t xs0, int64_t xs1, int64_t ws0, int64_t bs0, int64_t ys0, int64_t ys1,
+                      float inverse_features, float epsilon, int dtype, int64_t workers) {
+  struct layer_norm_args a = {x, w, b, y, n, xs0, xs1, ws0, bs0, ys0, ys1,
+                              inverse_features, epsilon, dtype};
+  dispatch_team(layer_norm_rows, &a, m, workers);
+  return ORACLE_OK;
+}
+
+/* ======================================================================== */
+/* a3  gemm (f16, optional ReLU) / bf16_gemm        gemm.py:54-92            */
+/*     c[m,n] = cast( Σ_k a[m,k]·b[k,n] ), inputs widened exactly, one       */
+/*     ascending-K fused multiply-add chain per output (Matrix.cpp:395-413). */
+/* ======================================================================== */
+struct gemm_args {
+  const uint16_t *a, *b; uint16_t *c;
+  int64_t n, k, as0, as1, bs0, bs1, cs0, cs1;
+  int dtype, relu;
+  int64_t row_begin; /* first logical row handled by this call */
+};
+
+#define GEMM_NB 64
+
+static void gemm_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct gemm_args *g = opaque;
+  const int64_t K = g->k, N = g->n;
+  /* Pack a K x GEMM_NB panel of B widened to f32, then stream rows of A over
+     it; every output keeps its own ascending-K chain. */
+  float *panel = malloc(sizeof(float) * (size_t)(K > 0 ? K : 1) * GEMM_NB);
+  float *arow = malloc(sizeof(float) * (size_t)(K > 0 ? K : 1));
+  for (int64_t n0 = 0; n0 < N; n0 += GEMM_NB) {
+    int64_t nb = N - n0 < GEMM_NB ? N - n0 : GEMM_NB;
+    for (int64_t k = 0; k < K; ++k)
+      for (int64_t j = 0; j < GEMM_NB; ++j)
+        panel[k * GEMM_NB + j] = j < nb
+          ? (g->dtype == DT_F16 ? f16_to_f32(g->b[k * g->bs0 + (n0 + j) * g->bs1])
+                                : bf16_to_f32(g->b[k * g->bs0 + (n0 + j) * g->bs1]))
+          : 0.0f;
+    for (int64_t m = begin; m < end; ++m) {
+      for (int64_t k = 0; k < K; ++k)
+        arow[k] = g->dtype == DT_F16 ? f16_to_f32(g->a[m * g->as0 + k * g->as1])
+                                     : bf16_to_f32(g->a[m * g->as0 + k * g->as1]);
+      float acc[GEMM_NB];
+      for (int j = 0; j < GEMM_NB; ++j) acc[j] = 0.0f;
+      for (int64_t k = 0; k < K; ++k) {
+        const float av = arow[k];
+        const float *bp = panel + k * GEMM_NB;
+        for (int j = 0; j < GEMM_NB; ++j) acc[j] = fmaf(av, bp[j], acc[j]);
+      }
+      for (int64_t j = 0; j < nb; ++j) {
+        float v = acc[j];
+        if (g->relu) v = (v != v) ? v : (v > 0.0f ? v : 0.0f); /* I.maximum propagates NaN */
+        g->c[m * g->cs0 + (n0 + j) * g->cs1] = g->dtype == DT_F16 ? f32_to_f16(v) : f32_to_bf16(v);
+      }
+    }
+  }
+  free(arow);
+  free(panel);
+}
+
+/* Computes rows [row_begin, row_begin + rows) of C; a and c point at logical
+   row 0 so a caller can time a bounded row sample of a large problem. */
+int oracle_gemm(const void *a, const void *b, void *c, int64_t row_begin, int64_t rows, int64_t n,
+                int64_t k, int64_t as0, int64_t as1, int64_t bs0, int64_t bs1, int64_t cs0,
+                int64_t cs1, int dtype, int relu, int64_t workers) {
+  struct gemm_args g = {a, b, c, n, k, as0, as1, bs0, bs1, cs0, cs1, dtype, relu, row_begin};
+  /* shift the base pointers instead of threading row_begin through the task */
+  g.a = (const uint16_t *)a + row_begin * as0;
+  g.c = (uint16_t *)c + row_begin * cs0;
+  dispatch_team(gemm_rows, &g, rows, workers);
+  return ORACLE_OK;
+}
+
+/* ======================================================================== */
+/* a4  flash_attention_bf16_fwd / flash_attention_fwd / flash_gqa_attention  */
+/*     attention.py:428-553.  region_fold over the key axis: every slice of  */
+/*     `chunk` keys is summarised with its own local maximum                 */
+/*     (summarize_attention_chunk_*, :150-236), slices are merged left to    */
+/*     right (merge_attention_summaries, :82-114), the final summary is      */
+/*     normalised (:417-425).  Slice size is compiler-chosen and             */
+/*     unobservable (core.en.md:193,212); the caller picks it here.          */
+/*     A slice with no valid key yields the neutral summary and merging it   */
+/*     is the identity in exact arithmetic and in f32 (1·x + 0·0), so such   */
+/*     slices are skipped.                                                   */
+/* ======================================================================== */
+struct attention_args {
+  const uint16_t *q, *k, *v; uint16_t *o;
+  int64_t hq, hk, sq, sk, d, dv;
+  int64_t qs[4], ks[4], vs[4], os[4];
+  float scale;
+  int64_t head_group;
+  int causal, dtype;
+  int64_t chunk;
+  int64_t unit_begin; /* first flattened (batch*HQ + head) unit */
+};
+
+static inline float half_to_f32(uint16_t h, int dtype) {
+  return dtype == DT_F16 ? f16_to_f32(h) : bf16_to_f32(h);
+}
+static inline float round_through_half(float f, int dtype) {
+  return dtype == DT_F16 ? f16_to_f32(f32_to_f16(f)) : bf16_to_f32(f32_to_bf16(f));
+}
+
+static void attention_units(void *opaque, int64_t begin, int64_t end) {
+  const struct attention_args *a = opaque;
+  const int64_t SK = a->sk, SQ = a->sq, D = a->d, DV = a->dv, C = a->chunk;
+  /* LOG2E is a double literal folded into the f32 scalar: scale * I.LOG2E */
+  const float score_scale = a->scale * (float)1.4426950408889634;
+  float *kt = malloc(sizeof(float) * (size_t)(D * SK > 0 ? D * SK : 1));  /* [d][key] */
+  float *vf = malloc(sizeof(float) * (size_t)(SK * DV > 0 ? SK * DV : 1)); /* [key][dv] */
+  float *scores = malloc(sizeof(float) * (size_t)C);
+  float *weights = malloc(sizeof(float) * (size_t)C);
+  float *acc = malloc(sizeof(float) * (size_t)DV);
+  float *chunk_acc = malloc(sizeof(float) * (size_t)DV);
+  float *qrow = malloc(sizeof(float) * (size_t)(D > 0 ? D : 1));
+  for (int64_t unit = begin + a->unit_begin; unit < end + a->unit_begin; ++unit) {
+    int64_t batch = unit / a->hq, head = unit % a->hq;
+    int64_t key_head = head / a->head_group; /* attention.py:531 */
+    const uint16_t *kb = a->k + batch * a->ks[0] + key_head * a->ks[1];
+    const uint16_t *vb = a->v + batch * a->vs[0] + key_head * a->vs[1];
+    for (int64_t j = 0; j < SK; ++j) {
+      for (int64_t d = 0; d < D; ++d) kt[d * SK + j] = half_to_f32(kb[j * a->ks[2] + d * a->ks[3]], a->dtype);
+      for (int64_t d = 0; d < DV; ++d) vf[j * DV + d] = half_to_f32(vb[j * a->vs[2] + d * a->vs[3]], a->dtype);
+    }
+    for (int64_t i = 0; i < SQ; ++i) {
+      const uint16_t *qp = a->q + batch * a->qs[0] + head * a->qs[1] + i * a->qs[2];
+      for (int64_t d = 0; d < D; ++d) qrow[d] = half_to_f32(qp[d * a->qs[3]], a->dtype);
+      int valid = 0;
+      float maximum = 0.0f, denominator = 0.0f;
+      for (int64_t d = 0; d < DV; ++d) acc[d] = 0.0f;
+      for (int64_t c0 = 0; c0 < SK; c0 += C) {
+        int64_t cn = SK - c0 < C ? SK - c0 : C;
+        int64_t live = cn;             /* keys with query >= key, a prefix of the slice */
+        if (a->causal) {
+          live = i - c0 + 1;
+          if (live <= 0) continue;     /* neutral summary */
+          if (live > cn) live = cn;
+        }
+        /* scores = matmul(q, k^T, acc f32) * (scale * LOG2E) */
+        for (int64_t j = 0; j < live; ++j) scores[j] = 0.0f;
+        for (int64_t d = 0; d < D; ++d) {
+          const float qv = qrow[d];
+          const float *kp = kt + d * SK + c0;
+          for (int64_t j = 0; j < live; ++j) scores[j] = fmaf(qv, kp[j], scores[j]);
+        }
+        float chunk_max = -INFINITY;
+        for (int64_t j = 0; j < live; ++j) {
+          scores[j] = scores[j] * score_scale;
+          chunk_max = maximum_num(chunk_max, scores[j]);
+        }
+        float chunk_den = 0.0f;
+        {
+          float lane[LANES];
+          for (int t = 0; t < LANES; ++t) lane[t] = 0.0f;
+          for (int64_t j = 0; j < live; ++j) {
+            float p = exp2_approx_ftz(scores[j] - chunk_max);
+            lane[j % LANES] = lane[j % LANES] + p;        /* denominator sums f32 p */
+            weights[j] = round_through_half(p, a->dtype); /* p is narrowed before P·V */
+          }
+          chunk_den = lanes_sum(lane);
+        }
+        for (int64_t d = 0; d < DV; ++d) chunk_acc[d] = 0.0f;
+        for (int64_t j = 0; j < live; ++j) {
+          const float w = weights[j];
+          const float *vp = vf + (c0 + j) * DV;
+          for (int64_t d = 0; d < DV; ++d) chunk_acc[d] = fmaf(w, vp[d], chunk_acc[d]);
+        }
+        /* merge_attention_summaries(lhs = running, rhs = this slice); rhs.valid */
+        float merged = valid ? maximum_num(maximum, chunk_max) : chunk_max;
+        float lhs_scale = valid ? exp2_approx_ftz(maximum - merged) : 0.0f;
+        float rhs_scale = exp2_approx_ftz(chunk_max - merged);
+        denominator = lhs_scale * denominator + rhs_scale * chunk_den;
+        for (int64_t d = 0; d < DV; ++d) acc[d] = lhs_scale * acc[d] + rhs_scale * chunk_acc[d];
+        maximum = merged;
+        valid = 1;
+      }
+      /* normalize_attention_summary + narrowing cast */
+      float inverse = fdiv_approx_ftz(1.0f, valid ? denominator : 1.0f);
+      uint16_t *op = a->o + batch * a->os[0] + head * a->os[1] + i * a->os[2];
+      for (int64_t d = 0; d < DV; ++d) {
+        float value = valid ? acc[d] * inverse : 0.0f;
+        op[d * a->os[3]] = a->dtype == DT_F16 ? f32_to_f16(value) : f32_to_bf16(value);
+      }
+    }
+  }
+  free(qrow); free(chunk_acc); free(acc); free(weights); free(scores); free(vf); free(kt);
+}
+
+/* Computes flattened (batch, query head) units [unit_begin, unit_begin+units). */
+int oracle_attention(const void *q, const void *k, const void *v, void *o, int64_t batch, int64_t hq,
+                     int64_t hk, int64_t sq, int64_t sk, int64_t d, int64_t dv, const int64_t *qs,
+                     const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
+                     int64_t head_group, int causal, int dtype, int64_t chunk, int64_t unit_begin,
+                     int64_t units, int64_t workers) {
+  (void)batch;
+  if (chunk <= 0 || head_group <= 0) return ORACLE_BAD_INDEX;
+  struct attention_args a = {.q = q, .k = k, .v = v, .o = o, .hq = hq, .hk = hk, .sq = sq, .sk = sk,
+                             .d = d, .dv = dv, .scale = scale, .head_group = head_group,
+                             .causal = causal, .dtype = dtype, .chunk = chunk,
+                             .unit_begin = unit_begin};
+  memcpy(a.qs, qs, sizeof a.qs); memcpy(a.ks, ks, sizeof a.ks);
+  memcpy(a.vs, vs, sizeof a.vs); memcpy(a.os, os, sizeof a.os);
+  dispatch_team(attention_units, &a, units, workers);
+  return ORACLE_OK;
+}
+
+/* ======================================================================== */
+/* a5  csr_spmm   csr_spmm.py:12-33.  Ordinary loop with a carried           */
+/*     accumulator: strict source order, one multiply then one add per term  */
+/*     (no fused multiply-add on the CPU provider).                          */
+/* ======================================================================== */
+struct spmm_args {
+  const int32_t *row_offsets, *column_indices; const float *values, *dense; float *output;
+  int64_t features, ds0, ds1, os0, os1;
+};
+
+static void spmm_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct spmm_args *s = opaque;
+  float *acc = malloc(sizeof(float) * (size_t)(s->features > 0 ? s->features : 1));
+  for (int64_t r = begin; r < end; ++r) {
+    for (int64_t f = 0; f < s->features; ++f) acc[f] = 0.0f;
+    for (int32_t nz = s->row_offsets[r]; nz < s->row_offsets[r + 1]; ++nz) {
+      const float value = s->values[nz];
+      const float *x = s->dense + (int64_t)s->column_indices[nz] * s->ds0;
+      for (int64_t f = 0; f < s->features; ++f) acc[f] = acc[f] + value * x[f * s->ds1];
+    }
+    for (int64_t f = 0; f < s->features; ++f) s->output[r * s->os0 + f * s->os1] = acc[f];
+  }
+  free(acc);
+}
+
+/* Validates what `assume_in_bounds` (csr_spmm.py:26-29) lets the kernel take
+   for granted: monotone offsets inside [0, nnz] and columns inside the dense
+   operand.  Returns ORACLE_BAD_INDEX and the first offending position. */
+int oracle_csr_validate(const int32_t *row_offsets, const int32_t *column_indices, int64_t rows,
+                        int64_t nnz, int64_t columns, int64_t *where) {
+  if (rows < 0) return ORACLE_BAD_INDEX;
+  if (row_offsets[0] < 0) { if (where) *where = 0; return ORACLE_BAD_INDEX; }
+  for (int64_t r = 0; r < rows; ++r)
+    if (row_offsets[r + 1] < row_offsets[r] || row_offsets[r + 1] > nnz) {
+      if (where) *where = r + 1;
+      return ORACLE_BAD_INDEX;
+    }
+  for (int64_t i = row_offsets[0]; i < row_offsets[rows]; ++i)
+    if (column_indices[i] < 0 || column_indices[i] >= columns) {
+      if (where) *where = i;
+      return ORACLE_BAD_INDEX;
+    }
+  return ORACLE_OK;
+}
+
+/* Computes rows [row_begin, row_begin+rows) of the output. */
+int oracle_csr_spmm(const int32_t *row_offsets, const int32_t *column_indices, const float *values,
+                    const float *dense, float *output, int64_t row_begin, int64_t rows,
+                    int64_t features, int64_t ds0, int64_t ds1, int64_t os0, int64_t os1,
+                    int64_t workers) {
+  struct spmm_args s = {row_offsets + row_begin, column_indices, values, dense,
+                        output + row_begin * os0, features, ds0, ds1, os0, os1};
+  dispatch_team(spmm_rows, &s, rows, workers);
+  return ORACLE_OK;
+}
+
+/* ---- timing helper for the CPU baseline --------------------------------- */
+/* Mirrors the CPU provider's benchmark export: the cache-eviction memset sits
+   outside the timed interval (runtime/mojo/compilation.py:34, 76-82). */
+double oracle_now_ms(void) {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+}
+void oracle_evict(void *buffer, int64_t bytes) { memset(buffer, 0, (size_t)bytes); }
+int oracle_max_workers(void) {
+  cpu_set_t allowed;
+  if (sched_getaffinity(0, sizeof allowed, &allowed) != 0) return 1;
+  return CPU_COUNT(&allowed);
+}
