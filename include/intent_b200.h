@@ -1,0 +1,161 @@
+/*
+ * intent_b200 — C ABI of the B200 (sm_100a) operator provider for IntentDSL.
+ *
+ * Every operator entry follows the reference's native slot convention
+ * (lib/Serialization/NativeABI.cpp:80-118; ctypes carriers in
+ * python/intent/runtime/native.py:15-17): for each public parameter, in
+ * declaration order,
+ *     view   ->  void* aP, int64 aP_d0.., int64 aP_s0..   (extents, then element strides)
+ *     scalar ->  its carrier (f32 -> float)
+ * followed by invocation workspaces (same view layout), and then a
+ * provider-private tail the reference's CPU entries do not have:
+ *     int32 constants taken from the kernel's constexprs / element type, and
+ *     void* stream  — the cudaStream_t to enqueue on (the caller passes the
+ *                     framework's current stream; nothing here synchronises,
+ *                     doc/getting-started/usage.en.md:53-55).
+ * The reference's CPU entries return void (python/intent/runtime/mojo/program.py:302-304);
+ * these return an int status instead of aborting, so a failing call never
+ * takes the process down and never falls back to another provider
+ * (doc/getting-started/usage.en.md:21).
+ *
+ * All pointers are device pointers on the current CUDA device.  The caller
+ * owns every buffer and keeps it alive until the stream has run the work
+ * (doc/getting-started/usage.en.md:50).
+ */
+#ifndef INTENT_B200_H
+#define INTENT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* status codes */
+#define B200_OK 0
+#define B200_ERR_INVALID_ARGUMENT 1   /* null pointer, negative extent, inconsistent shapes */
+#define B200_ERR_UNSUPPORTED_LAYOUT 2 /* strides / alignment / sizes this entry does not accept */
+#define B200_ERR_CUDA 3               /* a CUDA call failed; see b200_last_error */
+#define B200_ERR_DEVICE 4             /* not an sm_100 device */
+#define B200_ERR_DEVICE_TIMEOUT 5     /* a bounded device-side wait gave up (workspace status word) */
+
+/* element type codes of the private tail */
+#define B200_F32 0
+#define B200_F16 1
+#define B200_BF16 2
+
+/* Number of int32 words every workspace view must hold (zero-initialised by
+   the caller once; word 0 is a sticky device-side status, see b200_workspace_status). */
+#define B200_WORKSPACE_WORDS 64
+
+int b200_abi_version(void);
+const char *b200_status_string(int status);
+/* Copies the message of the most recent failing call on this thread. */
+int b200_last_error(char *buffer, int64_t capacity);
+/* B200_OK when `device` is an sm_100 part this library has code for. */
+int b200_device_check(int device);
+
+/*
+ * Row softmax.  Replaces the kernel the reference generates for
+ * stable_softmax / stable_softmax_f16 / chunked_softmax_bf16
+ * (python/intent/examples/kernels/normalization/softmax.py:23-66), i.e. the
+ * call made at python/intent/runtime/mojo/program.py:198-207 (CPU provider) or
+ * python/intent/runtime/triton/program.py:370-389 (GPU provider).
+ * f32: y = exp(x - max) * (1 / sum); f16/bf16: y = cast(exp(x - max) / sum).
+ * Requires unit inner strides (x_s1 == y_s1 == 1); row pitches are free.
+ */
+int b200_softmax(const void *x, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
+                 void *y, int64_t y_d0, int64_t y_d1, int64_t y_s0, int64_t y_s1,
+                 int32_t dtype, void *stream);
+
+/*
+ * LayerNorm forward.  Replaces layer_norm_f16 / layer_norm_bf16 (centred
+ * two-pass variance) and weighted_layer_norm (f32, E[x^2] - mean^2)
+ * (python/intent/examples/kernels/normalization/layer_norm.py:9-85).
+ * Statistics in f32; `centered` selects the variance form (1 for the 16-bit
+ * kernels, 0 for weighted_layer_norm).  Requires unit inner strides.
+ */
+int b200_layer_norm(const void *x, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
+                    const void *weight, int64_t w_d0, int64_t w_s0,
+                    const void *bias, int64_t b_d0, int64_t b_s0,
+                    void *y, int64_t y_d0, int64_t y_d1, int64_t y_s0, int64_t y_s1,
+                    float inverse_features, float epsilon,
+                    int32_t dtype, int32_t centered, void *stream);
+
+/*
+ * Dense GEMM C = cast(A . B), f16 or bf16 operands, f32 accumulation on the
+ * tcgen05 tensor cores.  Replaces gemm (ACTIVATION NONE / RELU) and bf16_gemm
+ * (python/intent/examples/kernels/contraction/gemm.py:54-92).
+ * a is (M,K), b is (K,N), c is (M,N) in element strides.  Accepted layouts:
+ * a K-major (a_s1 == 1), b K-major (b_s0 == 1, "column-major B") or N-major
+ * (b_s1 == 1), c row-major (c_s1 == 1); leading strides multiples of 8
+ * elements and 16-byte aligned bases (TMA requirements).
+ * workspace: B200_WORKSPACE_WORDS int32 words, zeroed once by the caller.
+ */
+int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a_s1,
+              const void *b, int64_t b_d0, int64_t b_d1, int64_t b_s0, int64_t b_s1,
+              void *c, int64_t c_d0, int64_t c_d1, int64_t c_s0, int64_t c_s1,
+              void *workspace, int64_t ws_d0, int64_t ws_s0,
+              int32_t dtype, int32_t relu, void *stream);
+
+/*
+ * Flash-attention forward (online softmax over key tiles), bf16 or f16.
+ * Replaces flash_attention_bf16_fwd, flash_attention_fwd and
+ * flash_gqa_attention_fwd
+ * (python/intent/examples/kernels/streaming/attention.py:428-553).
+ * q (B,HQ,Q,D), k (B,HK,K,D), v (B,HK,K,DV), o (B,HQ,Q,DV); key head =
+ * query head / head_group.  exp2 and the final reciprocal use
+ * ex2.approx.ftz / div.approx.ftz as the reference's NVIDIA target does
+ * (lib/Target/NVIDIA/IR/Target.cpp:62-86).  Requires unit innermost strides,
+ * D == DV == 128 (64 also accepted), other strides multiples of 8 elements.
+ */
+int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
+                         int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,
+                         const void *k, int64_t k_d0, int64_t k_d1, int64_t k_d2, int64_t k_d3,
+                         int64_t k_s0, int64_t k_s1, int64_t k_s2, int64_t k_s3,
+                         const void *v, int64_t v_d0, int64_t v_d1, int64_t v_d2, int64_t v_d3,
+                         int64_t v_s0, int64_t v_s1, int64_t v_s2, int64_t v_s3,
+                         void *o, int64_t o_d0, int64_t o_d1, int64_t o_d2, int64_t o_d3,
+                         int64_t o_s0, int64_t o_s1, int64_t o_s2, int64_t o_s3,
+                         float scale,
+                         void *workspace, int64_t ws_d0, int64_t ws_s0,
+                         int32_t dtype, int32_t head_group, int32_t causal, void *stream);
+
+/*
+ * CSR SpMM  Y = A . X, i32 indices, f32 values, strict source-order
+ * accumulation per row with an unfused multiply then add, so results are
+ * bit-identical to a sequential left-to-right evaluation.  Replaces csr_spmm
+ * (python/intent/examples/kernels/sparse/csr_spmm.py:12-33).
+ * Indices are trusted as the kernel's assume_in_bounds states
+ * (csr_spmm.py:26-29); b200_csr_validate checks them on the device.
+ * Requires contiguous index/value arrays and unit inner strides of X and Y.
+ */
+int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
+                  const void *column_indices, int64_t ci_d0, int64_t ci_s0,
+                  const void *values, int64_t va_d0, int64_t va_s0,
+                  const void *dense, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
+                  void *output, int64_t y_d0, int64_t y_d1, int64_t y_s0, int64_t y_s1,
+                  void *stream);
+
+/*
+ * Device-side check of a CSR structure (monotone offsets within [0,nnz],
+ * columns within [0,columns)).  No counterpart entry in the reference, whose
+ * kernel assumes validity (csr_spmm.py:26-29).  Synchronises the stream.
+ * Returns B200_OK or B200_ERR_INVALID_ARGUMENT with *where = first bad position.
+ */
+int b200_csr_validate(const void *row_offsets, int64_t rows, const void *column_indices,
+                      int64_t nnz, int64_t columns, int64_t *where, void *stream);
+
+/*
+ * Reads word 0 of a workspace after synchronising `stream`: B200_OK, or
+ * B200_ERR_DEVICE_TIMEOUT when a bounded wait inside a kernel gave up.
+ * `detail` (may be null) receives word 1, which names the wait that ran out.
+ */
+int b200_workspace_status(const void *workspace, int32_t *detail, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INTENT_B200_H */

@@ -1,0 +1,103 @@
+"""In-tree build of the native parts: the CUDA library and the compile step.
+
+``python -m intent_b200.build`` compiles
+
+* ``intent_b200/csrc/*.cu``  -> ``intent_b200/lib/libintent_b200.so``  (nvcc, sm_100a only)
+* ``intent_b200/compiler/b200_compile.cpp`` -> ``intent_b200/bin/b200-compile`` (g++)
+
+nvcc cross-compiles without a GPU, so this runs anywhere the CUDA toolkit is
+installed.  Objects are cached under ``build/`` and reused while their sources
+(and the shared headers) are older.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PACKAGE = Path(__file__).resolve().parent
+ROOT = PACKAGE.parent
+CSRC = PACKAGE / "csrc"
+LIBRARY = PACKAGE / "lib" / "libintent_b200.so"
+COMPILER = PACKAGE / "bin" / "b200-compile"
+OBJECTS = ROOT / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(found).exists():
+        raise RuntimeError("nvcc was not found; the CUDA toolkit is required to build intent_b200")
+    return found
+
+
+def _stale(target: Path, sources: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    stamp = target.stat().st_mtime
+    return any(source.stat().st_mtime > stamp for source in sources)
+
+
+def _run(command: list[str]) -> str:
+    completed = subprocess.run(command, capture_output=True, text=True)
+    if completed.returncode:
+        raise RuntimeError(f"{' '.join(command)}\n{completed.stdout}{completed.stderr}")
+    return completed.stdout + completed.stderr
+
+
+def build_library(*, force: bool = False, verbose: bool = False, resource_usage: bool = False) -> Path:
+    sources = sorted(CSRC.glob("*.cu"))
+    headers = sorted(CSRC.glob("*.cuh")) + [ROOT / "include" / "intent_b200.h"]
+    OBJECTS.mkdir(parents=True, exist_ok=True)
+    LIBRARY.parent.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+
+    def compile_one(source: Path) -> tuple[Path, str]:
+        target = OBJECTS / (source.stem + ".o")
+        log = ""
+        if force or resource_usage or _stale(target, [source, *headers]):
+            flags = NVCC_FLAGS + (["-Xptxas", "-v"] if resource_usage else [])
+            log = _run([nvcc, *flags, "-c", str(source), "-o", str(target)])
+        return target, log
+
+    with ThreadPoolExecutor(max_workers=min(8, len(sources) or 1)) as pool:
+        results = list(pool.map(compile_one, sources))
+    objects = [target for target, _ in results]
+    if verbose or resource_usage:
+        for _, log in results:
+            if log.strip():
+                print(log)
+    if force or _stale(LIBRARY, objects):
+        _run([nvcc, "-shared", "-o", str(LIBRARY), *map(str, objects), "-gencode",
+              "arch=compute_100a,code=sm_100a"])
+    return LIBRARY
+
+
+def build_compiler(*, force: bool = False) -> Path:
+    source = PACKAGE / "compiler" / "b200_compile.cpp"
+    COMPILER.parent.mkdir(parents=True, exist_ok=True)
+    if force or _stale(COMPILER, [source]):
+        _run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-Wextra", "-o",
+              str(COMPILER), str(source)])
+    return COMPILER
+
+
+def build_all(*, force: bool = False, verbose: bool = False) -> None:
+    build_library(force=force, verbose=verbose)
+    build_compiler(force=force)
+
+
+if __name__ == "__main__":
+    arguments = set(sys.argv[1:])
+    if "--resource-usage" in arguments:
+        build_library(force=True, resource_usage=True)
+    else:
+        build_all(force="--force" in arguments, verbose=True)
+    print(LIBRARY)

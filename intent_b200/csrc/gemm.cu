@@ -1,0 +1,377 @@
+// Dense GEMM  C[M,N] = cast(A[M,K] . B[K,N])  on the tcgen05 tensor cores.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: A (128 x 64) and B (256 x 64) K-major tiles,
+//               128-byte swizzled, into a kStages-deep shared-memory ring
+//   warp 1      MMA issuer: tcgen05.mma 128x256x16 (kind::f16, f32 accumulate)
+//               into one of two 256-column TMEM accumulators
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, convert,
+//               store C; runs while the next tile's main loop fills the
+//               other accumulator
+// mbarriers: full/empty per ring stage, full/empty per accumulator.  Every
+// wait is bounded (see tc::mbar_wait); a wait that gives up raises the status
+// word in the caller's workspace and the CTA drains and exits.
+//
+// Work per launch: 2*M*N*K flop; compulsory traffic (M*K + K*N + M*N)*2 bytes.
+// Tiles are walked in groups of kGroupM row-tiles per B column-tile so the
+// CTAs running together share A/B panels through L2.
+#include <mutex>
+#include <type_traits>
+#include <unordered_map>
+
+#include "tc.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;   // one 128-byte swizzle span of 16-bit elements
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kAccumulators = 2;
+constexpr int kTmemColumns = kAccumulators * kBlockN;  // 512
+constexpr int kGroupM = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+
+constexpr uint32_t kBytesA = kBlockM * kBlockK * 2;
+constexpr uint32_t kBytesB = kBlockN * kBlockK * 2;
+constexpr uint32_t kStageBytes = kBytesA + kBytesB;
+
+struct __align__(8) Barriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[kAccumulators];
+  uint64_t tmem_empty[kAccumulators];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes + sizeof(Barriers);
+
+struct TileWalk {
+  int tiles_m, tiles_n, total;
+  __device__ void locate(int tile, int *m, int *n) const {
+    const int group_span = kGroupM * tiles_n;
+    const int group = tile / group_span;
+    const int first_m = group * kGroupM;
+    const int rows_in_group = min(kGroupM, tiles_m - first_m);
+    const int within = tile - group * group_span;
+    *m = first_m + within % rows_in_group;
+    *n = within / rows_in_group;
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <typename T, bool RELU>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            T *__restrict__ c, int64_t c_pitch, int m, int n, int k, int *status) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char *tiles = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+  Barriers *bars = reinterpret_cast<Barriers *>(tiles + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  TileWalk walk;
+  walk.tiles_m = (m + kBlockM - 1) / kBlockM;
+  walk.tiles_n = (n + kBlockN - 1) / kBlockN;
+  walk.total = walk.tiles_m * walk.tiles_n;
+  const int k_blocks = (k + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&bars->full[s], 1);
+      tc::mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < kAccumulators; ++a) {
+      tc::mbar_init(&bars->tmem_full[a], 1);
+      tc::mbar_init(&bars->tmem_empty[a], kEpilogueThreads / 32);
+    }
+    bars->abort_flag = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_descriptor(&map_a);
+    tc::tma_prefetch_descriptor(&map_b);
+  }
+  if (warp == 1) tc::tmem_alloc(&bars->tmem_base, kTmemColumns);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile int *abort_flag = &bars->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (tc::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued = 0;  // ring slots handed to TMA (for the drain below)
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < walk.total; tile += gridDim.x) {
+        int tm, tn;
+        walk.locate(tile, &tm, &tn);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!tc::mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) {
+            alive = false;
+            break;
+          }
+          unsigned char *slot = tiles + stage * kStageBytes;
+          tc::mbar_expect_tx(&bars->full[stage], kStageBytes);
+          tc::tma_load_2d(slot, &map_a, &bars->full[stage], kb * kBlockK, tm * kBlockM);
+          tc::tma_load_2d(slot + kBytesA, &map_b, &bars->full[stage], kb * kBlockK, tn * kBlockN);
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!alive) {
+        // Let copies already in flight land before the CTA's shared memory is released.
+        const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
+        for (uint32_t back = 1; back <= pending; ++back) {
+          const uint32_t slot_index = issued - back;
+          const uint32_t s = slot_index % kStages, ph = (slot_index / kStages) & 1;
+          const long long start = clock64();
+          while (!tc::mbar_try_wait(&bars->full[s], ph) && clock64() - start < tc::kWaitCycles / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::instr_desc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
+                                                    kBlockM, kBlockN);
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < walk.total; tile += gridDim.x) {
+        if (!tc::mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
+        tc::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!tc::mbar_wait(&bars->full[stage], phase, abort_flag, status, tc::kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          tc::tc_fence_after_sync();
+          const uint32_t a_address = tc::smem_u32(tiles + stage * kStageBytes);
+          const uint64_t desc_a = tc::smem_desc_k_major_sw128(a_address);
+          const uint64_t desc_b = tc::smem_desc_k_major_sw128(a_address + kBytesA);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // +32 bytes per K step inside the swizzle span = +2 in 16-byte units
+            tc::mma_f16_ss(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
+          }
+          tc::mma_commit(&bars->empty[stage]);  // frees the ring slot when these MMAs retire
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!alive) break;
+        tc::mma_commit(&bars->tmem_full[acc]);
+        if (++acc == kAccumulators) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int quadrant = warp & 3;  // TMEM lanes [32*quadrant, +32) belong to this warp
+    uint32_t acc = 0, acc_phase = 0;
+    for (int tile = blockIdx.x; tile < walk.total; tile += gridDim.x) {
+      int tm, tn;
+      walk.locate(tile, &tm, &tn);
+      if (!tc::mbar_wait(&bars->tmem_full[acc], acc_phase, abort_flag, status, tc::kSiteEpilogueTmemFull)) break;
+      tc::tc_fence_after_sync();
+      const int row = tm * kBlockM + quadrant * 32 + lane;
+      const int column0 = tn * kBlockN;
+      T *destination = c + (int64_t)row * c_pitch + column0;
+      const bool vector_ok = (c_pitch % 8 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kBlockN / 32; ++chunk) {
+        uint32_t v[32];
+        tc::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + acc * kBlockN + chunk * 32, v);
+        tc::tmem_load_wait();
+        if (row < m) {
+          const int column = column0 + chunk * 32;
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            f[i] = __uint_as_float(v[i]);
+            if (RELU) f[i] = (f[i] != f[i]) ? f[i] : fmaxf(f[i], 0.0f);
+          }
+          if (vector_ok && column + 32 <= n) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 packed;
+              packed.x = pack2<T>(f[q * 8 + 0], f[q * 8 + 1]);
+              packed.y = pack2<T>(f[q * 8 + 2], f[q * 8 + 3]);
+              packed.z = pack2<T>(f[q * 8 + 4], f[q * 8 + 5]);
+              packed.w = pack2<T>(f[q * 8 + 6], f[q * 8 + 7]);
+              *reinterpret_cast<uint4 *>(destination + chunk * 32 + q * 8) = packed;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (column + i < n) destination[chunk * 32 + i] = Element<T>::narrow(f[i]);
+          }
+        }
+      }
+      tc::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&bars->tmem_empty[acc]);
+      if (++acc == kAccumulators) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemColumns);
+  }
+}
+
+// C = 0 for an empty reduction (K == 0).
+template <typename T>
+__global__ void zero_fill_kernel(T *c, int64_t c_pitch, int m, int n) {
+  const int64_t total = (int64_t)m * n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    c[(i / n) * c_pitch + i % n] = Element<T>::narrow(0.0f);
+}
+
+// ---- tensor-map cache -------------------------------------------------------
+struct MapKey {
+  const void *base;
+  uint64_t d0, d1, stride;
+  uint32_t b0, b1;
+  bool operator==(const MapKey &o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    for (uint64_t v : {k.d0, k.d1, k.stride, (uint64_t)k.b0, (uint64_t)k.b1}) h = h * 1000003u ^ v;
+    return h;
+  }
+};
+
+int cached_map_2d(CUtensorMap *out, const void *base, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
+                  uint32_t box_inner, uint32_t box_outer) {
+  static std::mutex lock;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, inner, outer, stride_bytes, box_inner, box_outer};
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return B200_OK;
+  }
+  const uint64_t dims[2] = {inner, outer};
+  const uint64_t strides[1] = {stride_bytes};
+  const uint32_t box[2] = {box_inner, box_outer};
+  const int status = encode_tensor_map_16bit(out, base, 2, dims, strides, box, true);
+  if (status != B200_OK) return status;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return B200_OK;
+}
+
+template <typename T>
+int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, int64_t a_pitch,
+               int64_t b_pitch, int64_t c_pitch, int relu, int *status, cudaStream_t stream) {
+  if (k == 0) {
+    zero_fill_kernel<T><<<sm_count() * 4, 256, 0, stream>>>(c, c_pitch, (int)m, (int)n);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  }
+  CUtensorMap map_a, map_b;
+  int result = cached_map_2d(&map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)a_pitch * 2, kBlockK, kBlockM);
+  if (result != B200_OK) return result;
+  result = cached_map_2d(&map_b, b, (uint64_t)k, (uint64_t)n, (uint64_t)b_pitch * 2, kBlockK, kBlockN);
+  if (result != B200_OK) return result;
+  auto kernel = relu ? gemm_kernel<T, true> : gemm_kernel<T, false>;
+  static std::once_flag configured[4];
+  cudaError_t attribute_error = cudaSuccess;
+  std::call_once(configured[(std::is_same<T, __half>::value ? 0 : 2) + (relu ? 1 : 0)], [&] {
+    attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  });
+  B200_CUDA_TRY(attribute_error);
+  const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + kBlockN - 1) / kBlockN);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, c, c_pitch, (int)m, (int)n, (int)k, status);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace
+
+// ---- host: tensor-map encoder (driver entry point, no link-time libcuda) ----
+int encode_tensor_map_16bit(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                            const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128) {
+  typedef CUresult (*Encode)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                             const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = nullptr;
+  static std::once_flag once;
+  static cudaError_t lookup_error = cudaSuccess;
+  std::call_once(once, [] {
+    void *pointer = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    lookup_error = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &query);
+    if (lookup_error == cudaSuccess && query == cudaDriverEntryPointSuccess) encode = reinterpret_cast<Encode>(pointer);
+  });
+  if (!encode) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable (%s)", cudaGetErrorString(lookup_error));
+  cuuint32_t element_strides[5] = {1, 1, 1, 1, 1};
+  const CUresult result = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank, const_cast<void *>(base),
+                                 dims, strides_bytes, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "cuTensorMapEncodeTiled rejected the layout (CUresult %d)", (int)result);
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a_s1,
+                         const void *b, int64_t b_d0, int64_t b_d1, int64_t b_s0, int64_t b_s1,
+                         void *c, int64_t c_d0, int64_t c_d1, int64_t c_s0, int64_t c_s1,
+                         void *workspace, int64_t ws_d0, int64_t ws_s0,
+                         int32_t dtype, int32_t relu, void *stream) {
+  const int64_t m = a_d0, k = a_d1, n = b_d1;
+  if (m < 0 || n < 0 || k < 0 || b_d0 != k || c_d0 != m || c_d1 != n)
+    return fail(B200_ERR_INVALID_ARGUMENT, "gemm: a is %lldx%lld, b is %lldx%lld, c is %lldx%lld",
+                (long long)a_d0, (long long)a_d1, (long long)b_d0, (long long)b_d1, (long long)c_d0, (long long)c_d1);
+  if (m == 0 || n == 0) return B200_OK;
+  if (!c || (k > 0 && (!a || !b))) return fail(B200_ERR_INVALID_ARGUMENT, "gemm: null buffer");
+  if (!workspace || ws_d0 < B200_WORKSPACE_WORDS || (ws_d0 > 1 && ws_s0 != 1))
+    return fail(B200_ERR_INVALID_ARGUMENT, "gemm: workspace must hold %d contiguous int32 words", B200_WORKSPACE_WORDS);
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return fail(B200_ERR_INVALID_ARGUMENT, "gemm: element type %d is not f16/bf16", dtype);
+  if (n > 1 && c_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: c must be row-major (c_s1 == 1)");
+  if (k > 1 && a_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: a must be K-major (a_s1 == 1)");
+  if (k > 1 && b_s0 != 1)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: b must be K-major (b_s0 == 1, i.e. column-major (K,N))");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: extent exceeds int32");
+  // a 1-row / 1-column operand has a free leading stride; give TMA a legal one
+  const int64_t a_pitch = m > 1 ? a_s0 : (k + 7) / 8 * 8;
+  const int64_t b_pitch = n > 1 ? b_s1 : (k + 7) / 8 * 8;
+  if (k > 0 && (a_pitch % 8 || b_pitch % 8 || a_pitch < k || b_pitch < k || !aligned16(a) || !aligned16(b)))
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT,
+                "gemm: TMA needs 16-byte aligned bases and leading strides that are multiples of 8 elements and >= K");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_F16)
+    return gemm_typed<__half>((const __half *)a, (const __half *)b, (__half *)c, m, n, k, a_pitch, b_pitch, c_s0,
+                              relu, (int *)workspace, s);
+  return gemm_typed<__nv_bfloat16>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)c, m, n, k,
+                                   a_pitch, b_pitch, c_s0, relu, (int *)workspace, s);
+}
