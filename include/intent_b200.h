@@ -58,6 +58,15 @@ int b200_last_error(char *buffer, int64_t capacity);
 int b200_device_check(int device);
 
 /*
+ * The eight integer facts the reference reads through the CUDA driver in
+ * resolve_cuda_device (python/intent/targets/nvidia/device.py:6-59), in its
+ * order: multiprocessors, shared memory per multiprocessor, opt-in shared
+ * memory per block, registers per multiprocessor, threads per block, compute
+ * capability major, minor, single-to-double throughput ratio.
+ */
+int b200_device_capabilities(int device, int64_t *facts);
+
+/*
  * Row softmax.  Replaces the kernel the reference generates for
  * stable_softmax / stable_softmax_f16 / chunked_softmax_bf16
  * (python/intent/examples/kernels/normalization/softmax.py:23-66), i.e. the

@@ -40,6 +40,7 @@ SIGNATURES = {
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],
     "b200_device_check": [ctypes.c_int],
+    "b200_device_capabilities": [ctypes.c_int, ctypes.POINTER(_I64)],
     "b200_abi_version": [],
     "b200_last_error": [ctypes.c_char_p, _I64],
 }

@@ -83,3 +83,18 @@ extern "C" int b200_workspace_status(const void *workspace, int32_t *detail, voi
     return fail(B200_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (site %d)", words[1]);
   return B200_OK;
 }
+
+extern "C" int b200_device_capabilities(int device, int64_t *facts) {
+  if (!facts) return fail(B200_ERR_INVALID_ARGUMENT, "device_capabilities: null output");
+  const cudaDeviceAttr attributes[8] = {
+      cudaDevAttrMultiProcessorCount, cudaDevAttrMaxSharedMemoryPerMultiprocessor,
+      cudaDevAttrMaxSharedMemoryPerBlockOptin, cudaDevAttrMaxRegistersPerMultiprocessor,
+      cudaDevAttrMaxThreadsPerBlock, cudaDevAttrComputeCapabilityMajor,
+      cudaDevAttrComputeCapabilityMinor, cudaDevAttrSingleToDoublePrecisionPerfRatio};
+  for (int i = 0; i < 8; ++i) {
+    int value = 0;
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&value, attributes[i], device));
+    facts[i] = value;
+  }
+  return B200_OK;
+}

@@ -1,0 +1,661 @@
+"""Host runtime of the b200 provider: artifact.json -> binder -> prepared call -> C ABI.
+
+This module mirrors the part of the reference runtime that sits between a
+compiled program and its native entry, with the same names, argument meaning
+and error behaviour, but without importing the reference:
+
+===========================  =====================================================
+here                         reference
+===========================  =====================================================
+``Interface.read``           ``PublicInterface.read``   runtime/interface.py:110-150
+``Interface.relations``      ``binding_relations``      runtime/interface.py:187-245
+``NativeLayout.read``        ``NativeABI.read``         runtime/native.py:77-130
+``Requirements``             ``NativeRequirements``     runtime/native_requirements.py:21-91
+``B200Program``              ``NativePreparedRuntime``  runtime/native.py:240-273
+``B200Call``                 ``PreparedCall``           runtime/artifact.py:23-55
+``Artifact``                 ``CompiledArtifact``       runtime/artifact.py:94-218
+``register_operator``        same name                  integrations/torch.py:27-93
+===========================  =====================================================
+
+A launch is one ``ctypes`` call on torch's current CUDA stream and never
+synchronises; ``result()`` returns the output containers as they are
+(``doc/getting-started/usage.en.md:53-55``).  There is no fallback: if the CUDA
+library is missing or refuses the call, the error propagates.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from inspect import Parameter, Signature
+from threading import RLock
+
+import torch
+
+from . import _native
+
+IN, OUT, INOUT = 0, 1, 2
+
+TORCH_DTYPES = {
+    "index": torch.int64, "bool": torch.bool, "i8": torch.int8, "i16": torch.int16, "i32": torch.int32,
+    "i64": torch.int64, "u8": torch.uint8, "f16": torch.float16, "bf16": torch.bfloat16,
+    "f32": torch.float32, "f64": torch.float64,
+}
+_DTYPE_BYTES = {"bool": 1, "i8": 1, "u8": 1, "i16": 2, "f16": 2, "bf16": 2, "i32": 4, "f32": 4,
+                "i64": 8, "f64": 8, "index": 8}
+_CARRIERS = {"ptr": ctypes.c_void_p, "bool": ctypes.c_bool, "i8": ctypes.c_int8, "i16": ctypes.c_int16,
+             "i32": ctypes.c_int32, "i64": ctypes.c_int64, "f32": ctypes.c_float, "f64": ctypes.c_double}
+
+
+# --------------------------------------------------------------------------- interface
+@dataclass(frozen=True)
+class ScalarParameter:
+    position: int
+    name: str
+    dtype: str
+
+
+@dataclass(frozen=True)
+class StrideSymbol:
+    name: str
+
+
+@dataclass(frozen=True)
+class ViewParameter:
+    position: int
+    name: str
+    dtype: str
+    shape: tuple
+    dimensions: tuple
+    strides: tuple
+    access: int
+    alias: str
+    noalias: bool
+
+    @property
+    def writable(self) -> bool:
+        return self.access != IN
+
+    @property
+    def output(self) -> bool:
+        return self.access == OUT
+
+
+@dataclass(frozen=True)
+class ViewFacts:
+    """What one binding observed of a tensor (runtime/invocation.py:11-24)."""
+    shape: tuple
+    strides: tuple
+    pointer: int | None
+    allocation: tuple | None      # (begin, end) of the whole storage
+    span: tuple | None            # (begin, end) of the bytes this view can touch
+    identity: object
+
+
+def _byte_span(pointer: int, shape, strides, size: int) -> tuple[int, int]:
+    if any(extent == 0 for extent in shape):
+        return pointer, pointer
+    low = high = 0
+    for extent, stride in zip(shape, strides):
+        displacement = (extent - 1) * stride
+        low += min(0, displacement)
+        high += max(0, displacement)
+    return pointer + low * size, pointer + (high + 1) * size
+
+
+def _overlap(lhs, rhs) -> bool:
+    return lhs[0] < lhs[1] and rhs[0] < rhs[1] and lhs[0] < rhs[1] and rhs[0] < lhs[1]
+
+
+@dataclass(frozen=True)
+class Interface:
+    """The author's ordered runtime parameters, independent of the device ABI."""
+    parameters: tuple
+
+    @classmethod
+    def read(cls, metadata: dict) -> "Interface":
+        parameters, names = [], set()
+        for position, entry in enumerate(metadata["parameters"]):
+            name = entry["name"]
+            if not isinstance(name, str) or not name or name in names:
+                raise ValueError("public parameter names must be nonempty and unique")
+            names.add(name)
+            if entry["dtype"] not in _DTYPE_BYTES:
+                raise NotImplementedError(f"element type {entry['dtype']!r} is not supported by b200")
+            if entry["kind"] == "scalar":
+                parameters.append(ScalarParameter(position, name, entry["dtype"]))
+                continue
+            if entry["kind"] != "view":
+                raise ValueError("public interface parameter must be a view or scalar")
+            shape, dimensions = tuple(entry["shape"]), tuple(entry["dimensions"])
+            if any(type(extent) is not int or extent < -1 for extent in shape):
+                raise ValueError("public shape requires static extents or dynamic -1")
+            if len(dimensions) != len(shape):
+                raise ValueError("public dimension identities must match view rank")
+            strides = []
+            for constraint in entry["strides"]:
+                if constraint is None or type(constraint) is int:
+                    strides.append(constraint)
+                elif isinstance(constraint, dict) and constraint.get("kind") == "stride_symbol":
+                    strides.append(StrideSymbol(constraint["symbol"]))
+                else:
+                    raise ValueError("unsupported public stride constraint")
+            if len(strides) != len(shape):
+                raise ValueError("public stride constraints must match view rank")
+            if entry["alias"] and entry["noalias"]:
+                raise ValueError("alias and noalias are mutually exclusive")
+            if entry["access"] not in (IN, OUT, INOUT):
+                raise ValueError("public access must be 0 (In), 1 (Out) or 2 (InOut)")
+            parameters.append(ViewParameter(position, name, entry["dtype"], shape, dimensions,
+                                            tuple(strides), entry["access"], entry["alias"], entry["noalias"]))
+        return cls(tuple(parameters))
+
+    @property
+    def views(self):
+        return tuple(p for p in self.parameters if isinstance(p, ViewParameter))
+
+    @property
+    def inputs(self):
+        return tuple(p for p in self.parameters if not isinstance(p, ViewParameter) or not p.output)
+
+    @property
+    def outputs(self):
+        return tuple(p for p in self.views if p.output)
+
+    def explicit_arguments(self, arguments: tuple, outputs: tuple) -> tuple:
+        if len(arguments) != len(self.inputs):
+            raise TypeError(f"expected {len(self.inputs)} input arguments, got {len(arguments)}")
+        if len(outputs) != len(self.outputs):
+            raise TypeError(f"expected {len(self.outputs)} explicit output buffers, got {len(outputs)}")
+        supplied, allocated = iter(arguments), iter(outputs)
+        return tuple(next(allocated) if isinstance(p, ViewParameter) and p.output else next(supplied)
+                     for p in self.parameters)
+
+
+# --------------------------------------------------------------------------- native layout
+@dataclass(frozen=True)
+class Workspace:
+    position: int
+    dtype: str
+    shape: tuple
+
+
+@dataclass(frozen=True)
+class Slot:
+    parameter: int
+    role: str          # pointer | extent | stride | scalar
+    carrier: str
+    axis: int | None = None
+
+
+@dataclass(frozen=True)
+class ViewRequirement:
+    layout: str
+    alignment: int
+
+
+@dataclass(frozen=True)
+class Requirements:
+    views: dict
+    disjoint: frozenset
+
+    @classmethod
+    def read(cls, metadata: dict, interface: Interface) -> "Requirements":
+        try:
+            requirements = metadata["native"]["requirements"]
+        except KeyError as error:
+            raise ValueError("native artifact lacks explicit entry requirements") from error
+        views = {}
+        for entry in requirements["views"]:
+            position = entry["parameter"]
+            if (type(position) is not int or not 0 <= position < len(interface.parameters)
+                    or not isinstance(interface.parameters[position], ViewParameter) or position in views):
+                raise ValueError("native view requirement references an unknown or repeated public view")
+            if entry["layout"] not in {"strided", "contiguous"}:
+                raise ValueError("native entry has an unknown view layout requirement")
+            if type(entry["alignment"]) is not int or entry["alignment"] <= 0:
+                raise ValueError("native entry alignment must be a positive byte count")
+            views[position] = ViewRequirement(entry["layout"], entry["alignment"])
+        if any(view.position not in views for view in interface.views):
+            raise ValueError("native entry must declare requirements for every public view")
+        disjoint = set()
+        for entry in requirements["disjoint"]:
+            left, right = entry["left"], entry["right"]
+            if not (type(left) is int and type(right) is int and left < right and left in views and right in views):
+                raise ValueError("native disjointness requirement must name two ordered public views")
+            disjoint.add((left, right))
+        return cls(views, frozenset(disjoint))
+
+
+@dataclass(frozen=True)
+class NativeLayout:
+    interface: Interface
+    slots: tuple
+    workspaces: tuple
+    requirements: Requirements
+
+    @classmethod
+    def read(cls, metadata: dict) -> "NativeLayout":
+        interface = Interface.read(metadata["interface"])
+        workspaces = []
+        for entry in metadata["native"]["workspaces"]:
+            if entry["position"] != len(interface.parameters) + len(workspaces):
+                raise ValueError("native workspaces must follow the public arguments in declaration order")
+            workspaces.append(Workspace(entry["position"], entry["dtype"], tuple(entry["shape"])))
+        count = len(interface.parameters) + len(workspaces)
+        slots, seen = [], set()
+        for entry in metadata["native"]["slots"]:
+            position, role, carrier = entry["parameter"], entry["role"], entry["carrier"]
+            if type(position) is not int or not 0 <= position < count:
+                raise ValueError("native slot references an unknown entry parameter")
+            if carrier not in _CARRIERS:
+                raise NotImplementedError(f"native scalar carrier {carrier!r} is unsupported")
+            if role not in {"pointer", "extent", "stride", "scalar"}:
+                raise ValueError("unknown native slot role")
+            axis = entry.get("axis")
+            if (axis is not None) != (role in {"extent", "stride"}):
+                raise ValueError("native slot fields disagree with its role")
+            if (position, role, axis) in seen:
+                raise ValueError("native ABI has duplicate parameter slots")
+            seen.add((position, role, axis))
+            slots.append(Slot(position, role, carrier, axis))
+        for parameter in interface.parameters:
+            view = isinstance(parameter, ViewParameter)
+            if (parameter.position, "pointer" if view else "scalar", None) not in seen:
+                raise ValueError("native ABI does not bind every public parameter")
+            if view:
+                for axis in range(len(parameter.shape)):
+                    if any((parameter.position, role, axis) not in seen for role in ("extent", "stride")):
+                        raise ValueError("native ABI must bind the extent and stride of every view axis")
+        return cls(interface, tuple(slots), tuple(workspaces), Requirements.read(metadata, interface))
+
+
+@dataclass(frozen=True)
+class B200Facts:
+    """Provider-private section of artifact.json written by b200-compile."""
+    family: str
+    entry: str
+    tail: tuple          # ((name, carrier, value), ...)
+
+    @classmethod
+    def read(cls, metadata: dict) -> "B200Facts":
+        section = metadata["b200"]
+        if section.get("abi_version") != 1:
+            raise ValueError("artifact was produced for another intent_b200 ABI version")
+        if section["entry"] not in _native.SIGNATURES:
+            raise ValueError(f"artifact names an unknown entry {section['entry']!r}")
+        tail = tuple((item["name"], item["carrier"], item["value"]) for item in section["tail"])
+        return cls(section["family"], section["entry"], tail)
+
+
+@dataclass(frozen=True)
+class Observation:
+    """Per-call facts, the b200 analogue of the reference's NativeObservation
+    (runtime/diagnostics.py:22-144)."""
+    provider: str
+    family: str
+    entry: str
+    constants: tuple
+    stage: str
+    arguments: tuple
+
+
+# --------------------------------------------------------------------------- binding
+class _Abstract:
+    """Marker: bind shapes only (FakeTensor / meta tracing), never addresses."""
+
+
+def _relation(actual, expected, message: str, abstract: bool) -> None:
+    if abstract:
+        torch._check(actual == expected, lambda: message)
+    elif actual != expected:
+        raise ValueError(message)
+
+
+class B200Program:
+    """Binds torch tensors to one native entry; mirrors NativePreparedRuntime."""
+
+    device_type = "cuda"
+
+    def __init__(self, metadata: dict, device: int | torch.device):
+        if metadata.get("provider") != "b200":
+            raise ValueError("not a b200 program")
+        self.metadata = metadata
+        self.layout = NativeLayout.read(metadata)
+        self.interface = self.layout.interface
+        self.facts = B200Facts.read(metadata)
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self._observation: Observation | None = None
+        self._lock = RLock()
+        self._function = None
+        signature = _native.SIGNATURES[self.facts.entry]
+        expected = [_CARRIERS[slot.carrier] for slot in self.layout.slots]
+        expected += [_CARRIERS[carrier] for _, carrier, _ in self.facts.tail] + [ctypes.c_void_p]
+        if list(signature) != expected:
+            raise ValueError(f"artifact slots do not match the signature of {self.facts.entry}")
+
+    # -- observation ---------------------------------------------------------
+    @property
+    def observation(self) -> Observation | None:
+        return self._observation
+
+    @property
+    def configuration_descriptions(self):
+        return ({"family": self.facts.family, "entry": self.facts.entry,
+                 **{name: value for name, _, value in self.facts.tail}},)
+
+    def inspect_configurations(self):
+        return self.configuration_descriptions
+
+    # -- binder ----------------------------------------------------------------
+    def _observe(self, parameter: ViewParameter, value, abstract: bool) -> ViewFacts:
+        if not isinstance(value, torch.Tensor):
+            raise TypeError(f"{parameter.name} must be a torch.Tensor")
+        expected = TORCH_DTYPES[parameter.dtype]
+        if value.dtype != expected:
+            raise TypeError(f"{parameter.name} must have dtype {expected}, got {value.dtype}")
+        if not abstract and value.device != self.device:
+            raise ValueError(f"{parameter.name} must be on {self.device}, got {value.device}")
+        shape, strides = tuple(value.shape), tuple(value.stride())
+        if len(shape) != len(parameter.shape):
+            raise ValueError(f"{parameter.name} must have rank {len(parameter.shape)}, got {len(shape)}")
+        if abstract:
+            return ViewFacts(shape, strides, None, None, None, None)
+        storage = value.untyped_storage()
+        begin, size = storage.data_ptr(), storage.nbytes()
+        pointer = value.data_ptr()
+        identity = (value.device, begin) if size else (value.device, "empty", storage._cdata)
+        return ViewFacts(shape, strides, pointer, (begin, begin + size),
+                         _byte_span(pointer, shape, strides, value.element_size()), identity)
+
+    def _bind(self, arguments: tuple, explicit_outputs: bool, abstract: bool = False):
+        interface = self.interface
+        supplied = interface.parameters if explicit_outputs else interface.inputs
+        if len(arguments) != len(supplied):
+            raise TypeError(f"expected {len(supplied)} runtime arguments, got {len(arguments)}")
+        values: dict[int, object] = {}
+        facts: dict[int, ViewFacts] = {}
+        dimensions: dict[int, int] = {}
+        symbols: dict[str, int] = {}
+        static = {}
+        for view in interface.views:
+            for extent, identity in zip(view.shape, view.dimensions):
+                if extent >= 0 and identity > 0:
+                    known = static.setdefault(identity, extent)
+                    if known != extent and not explicit_outputs:
+                        raise NotImplementedError(
+                            f"Cannot allocate the declared outputs: dimension {identity} has conflicting "
+                            f"static extents {known} and {extent}. Provide explicit output buffers with "
+                            "prepare(..., outputs=(...)) or launch(...).")
+
+        def check(parameter: ViewParameter, observed: ViewFacts, allocated: bool) -> None:
+            for axis, (extent, identity) in enumerate(zip(parameter.shape, parameter.dimensions)):
+                message = f"{parameter.name}.shape[{axis}] violates the declared interface relation"
+                known = extent if extent >= 0 else static.get(identity)
+                if known is not None:
+                    _relation(observed.shape[axis], known, message, abstract)
+                if identity > 0:
+                    if identity in dimensions:
+                        _relation(observed.shape[axis], dimensions[identity], message, abstract)
+                    else:
+                        dimensions[identity] = observed.shape[axis]
+            for axis, constraint in enumerate(parameter.strides):
+                message = f"{parameter.name}.strides[{axis}] violates the declared interface relation"
+                if allocated:
+                    message += "; provide explicit output buffers with the required layout"
+                if isinstance(constraint, StrideSymbol):
+                    if constraint.name in symbols:
+                        _relation(observed.strides[axis], symbols[constraint.name], message, abstract)
+                    else:
+                        symbols[constraint.name] = observed.strides[axis]
+                elif constraint is not None:
+                    _relation(observed.strides[axis], constraint, message, abstract)
+            requirement = self.layout.requirements.views[parameter.position]
+            if requirement.layout == "contiguous":
+                expected = 1
+                for extent, stride in zip(reversed(observed.shape), reversed(observed.strides)):
+                    if abstract:
+                        torch._check(stride == expected, lambda: f"{parameter.name}: native entry requires "
+                                                                 "canonical contiguous element strides")
+                    elif stride != expected:
+                        raise NotImplementedError(
+                            f"{parameter.name}: native entry requires canonical contiguous element strides")
+                    expected *= extent
+            if not abstract and observed.pointer % requirement.alignment:
+                raise ValueError(
+                    f"{parameter.name}: native entry requires {requirement.alignment}-byte pointer alignment")
+
+        for position, parameter in enumerate(supplied):
+            values[parameter.position] = arguments[position]
+            if isinstance(parameter, ViewParameter):
+                facts[parameter.position] = self._observe(parameter, arguments[position], abstract)
+                check(parameter, facts[parameter.position], False)
+            elif isinstance(arguments[position], torch.Tensor):
+                raise TypeError(f"{parameter.name} is a scalar parameter, got a tensor")
+        if not explicit_outputs:
+            for parameter in interface.outputs:
+                shape = []
+                for axis, (extent, identity) in enumerate(zip(parameter.shape, parameter.dimensions)):
+                    known = extent if extent >= 0 else static.get(identity, dimensions.get(identity))
+                    if known is None:
+                        raise NotImplementedError(
+                            f"Cannot allocate the declared outputs: {parameter.name}.shape[{axis}] has no extent "
+                            "supplied by inputs or fixed by the public shape declarations. Provide explicit "
+                            "output buffers with prepare(..., outputs=(...)) or launch(...).")
+                    shape.append(known)
+                device = "meta" if abstract and not any(
+                    isinstance(v, torch.Tensor) for v in arguments) else (
+                    next(v.device for v in arguments if isinstance(v, torch.Tensor)) if abstract else self.device)
+                tensor = torch.empty(tuple(shape), dtype=TORCH_DTYPES[parameter.dtype], device=device)
+                values[parameter.position] = tensor
+                facts[parameter.position] = self._observe(parameter, tensor, abstract)
+                check(parameter, facts[parameter.position], True)
+        if not abstract:
+            views = interface.views
+            for index, left in enumerate(views):
+                for right in views[index + 1:]:
+                    lf, rf = facts[left.position], facts[right.position]
+                    names = f"{left.name} and {right.name}"
+                    if (left.noalias or right.noalias) and _overlap(lf.allocation, rf.allocation):
+                        raise ValueError(f"{names} violate an author noalias allocation constraint")
+                    if left.alias and left.alias == right.alias and lf.identity != rf.identity:
+                        raise ValueError(f"{names} violate an author named allocation-alias constraint")
+                    if ((left.position, right.position) in self.layout.requirements.disjoint
+                            and _overlap(lf.span, rf.span)):
+                        raise NotImplementedError(
+                            f"{names}: native entry requires nonoverlapping accessed byte spans")
+        ordered = tuple(values[p.position] for p in interface.parameters)
+        outputs = tuple(values[p.position] for p in interface.outputs)
+        return ordered, outputs, facts
+
+    def _native_arguments(self, ordered: tuple, facts: dict, workspaces: dict) -> tuple:
+        packed = []
+        for slot in self.layout.slots:
+            if slot.role == "scalar":
+                value = ordered[slot.parameter]
+                packed.append(float(value) if slot.carrier in {"f32", "f64"} else int(value))
+                continue
+            observed = facts[slot.parameter] if slot.parameter in facts else workspaces[slot.parameter]
+            if slot.role == "pointer":
+                packed.append(observed.pointer)
+            elif slot.role == "extent":
+                packed.append(observed.shape[slot.axis])
+            else:
+                packed.append(observed.strides[slot.axis])
+        packed.extend(value for _, _, value in self.facts.tail)
+        return tuple(packed)
+
+    # -- public preparation API --------------------------------------------------
+    def prepare(self, arguments: tuple, *, explicit_outputs: bool = False) -> "B200Call":
+        ordered, outputs, facts = self._bind(tuple(arguments), explicit_outputs)
+        owners, workspace_facts = [], {}
+        for workspace in self.layout.workspaces:
+            # invocation-owned, like the reference's workspaces (runtime/native.py:207-209)
+            tensor = torch.zeros(workspace.shape, dtype=TORCH_DTYPES[workspace.dtype], device=self.device)
+            owners.append(tensor)
+            workspace_facts[workspace.position] = ViewFacts(
+                tuple(tensor.shape), tuple(tensor.stride()), tensor.data_ptr(), None, None, None)
+        description = tuple(
+            (p.name, facts[p.position].shape, facts[p.position].strides) if isinstance(p, ViewParameter)
+            else (p.name, ordered[p.position]) for p in self.interface.parameters)
+        return B200Call(self, ordered, self._native_arguments(ordered, facts, workspace_facts), outputs,
+                        tuple(owners), description)
+
+    def prepare_call(self, arguments: tuple, *, outputs: tuple | None = None) -> "B200Call":
+        if outputs is None:
+            return self.prepare(arguments)
+        return self.prepare(self.interface.explicit_arguments(arguments, outputs), explicit_outputs=True)
+
+    def run(self, *arguments):
+        call = self.prepare(arguments)
+        call.launch()
+        return call.result()
+
+    def launch(self, *arguments) -> None:
+        self.prepare(arguments, explicit_outputs=True).launch()
+
+    def infer_outputs(self, arguments: tuple):
+        """Output containers for abstract (fake / meta) inputs; never touches addresses."""
+        _, outputs, _ = self._bind(tuple(arguments), False, abstract=True)
+        return None if not outputs else outputs[0] if len(outputs) == 1 else outputs
+
+    def function(self):
+        with self._lock:
+            if self._function is None:
+                self._function = _native.entry(self.facts.entry)
+            return self._function
+
+    def close(self) -> None:
+        self._function = None
+
+
+@dataclass
+class B200Call:
+    """Invocation-owned arguments and outputs (PreparedCall, runtime/artifact.py:23-55)."""
+    program: B200Program
+    arguments: tuple
+    native_arguments: tuple
+    outputs: tuple
+    workspaces: tuple
+    description: tuple
+    _observation: Observation | None = field(default=None, repr=False)
+
+    def compile(self) -> None:
+        """Nothing is JIT-compiled: validate that the AOT library holds the entry."""
+        self.program.function()
+        self._record("compiled")
+
+    def _record(self, stage: str) -> None:
+        facts = self.program.facts
+        self._observation = Observation("b200", facts.family, facts.entry, facts.tail, stage, self.description)
+        self.program._observation = self._observation
+
+    def launch(self) -> None:
+        function = self.program.function()
+        device = self.program.device
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            status = function(*self.native_arguments, stream)
+        if status != _native.OK:
+            self._record("failed")
+            _native.check(self.program.facts.entry, status)
+        self._record("launched")
+
+    def result(self):
+        if not self.outputs:
+            return None
+        return self.outputs[0] if len(self.outputs) == 1 else self.outputs
+
+    def check(self) -> None:
+        """Synchronise and raise if a bounded device-side wait gave up (tensor-core entries)."""
+        for workspace in self.workspaces:
+            detail = ctypes.c_int32(0)
+            with torch.cuda.device(self.program.device):
+                stream = torch.cuda.current_stream(self.program.device).cuda_stream
+                status = _native.entry("b200_workspace_status")(workspace.data_ptr(), ctypes.byref(detail), stream)
+            _native.check("b200_workspace_status", status)
+
+    @property
+    def observation(self) -> Observation | None:
+        return self._observation
+
+    def inspect_configurations(self):
+        return self.program.inspect_configurations()
+
+
+@dataclass
+class Artifact:
+    """What materialising a generated program yields (CompiledArtifact)."""
+    source: str
+    mlir: str
+    device: int
+    runtime: B200Program
+    device_type: str = "cuda"
+    cache_directory: object = None
+
+    @property
+    def interface(self) -> Interface:
+        return self.runtime.interface
+
+    @property
+    def observation(self):
+        return self.runtime.observation
+
+    @property
+    def ir(self) -> dict:
+        return {"intent": self.mlir}
+
+    def run(self, *arguments):
+        return self.runtime.run(*arguments)
+
+    def prepare(self, *arguments, outputs: tuple | None = None) -> B200Call:
+        return self.runtime.prepare_call(arguments, outputs=outputs)
+
+    def launch(self, *arguments) -> None:
+        self.runtime.launch(*arguments)
+
+    __call__ = launch
+
+    def inspect_configurations(self, *arguments, outputs: tuple | None = None):
+        return self.prepare(*arguments, outputs=outputs).inspect_configurations()
+
+    def as_torch_op(self, name: str):
+        return register_operator(self, name)
+
+
+# --------------------------------------------------------------------------- torch custom op
+def register_operator(artifact, name: str):
+    """Expose the artifact as a ``torch.library`` custom operator: schema from the
+    public inputs, fake implementation from ``infer_outputs`` (no execution)."""
+    interface = artifact.interface
+    inputs = interface.inputs
+    views = tuple((index, p) for index, p in enumerate(inputs) if isinstance(p, ViewParameter))
+    if not views:
+        raise NotImplementedError("PyTorch registration requires an input tensor to determine device dispatch")
+    pieces = name.split("::")
+    if len(pieces) != 2 or not all(piece.isidentifier() for piece in pieces):
+        raise ValueError("operator name must be 'your_namespace::your_operator'")
+    mutable = tuple(f"arg{index}" for index, p in views if p.writable)
+    parameters = []
+    for index, p in enumerate(inputs):
+        if isinstance(p, ViewParameter):
+            kind = f"Tensor(a{index}!)" if p.writable else "Tensor"
+        elif p.dtype == "bool":
+            kind = "bool"
+        elif p.dtype in {"f16", "bf16", "f32", "f64"}:
+            kind = "float"
+        else:
+            kind = "SymInt"
+        parameters.append(f"{kind} arg{index}")
+    returns = "Tensor" if len(interface.outputs) == 1 else "(" + ", ".join("Tensor" for _ in interface.outputs) + ")"
+    schema = f"({', '.join(parameters)}) -> {returns}"
+    signature = Signature(Parameter(f"arg{i}", Parameter.POSITIONAL_OR_KEYWORD) for i in range(len(parameters)))
+
+    def adapt(invoke):
+        def operator(*arguments, **keywords):
+            return invoke(*signature.bind(*arguments, **keywords).args)
+        return operator
+
+    operator = torch.library.custom_op(name, adapt(artifact.run), mutates_args=mutable,
+                                       device_types=artifact.device_type, schema=schema)
+    operator.register_fake(adapt(lambda *arguments: artifact.runtime.infer_outputs(arguments)))
+    return operator

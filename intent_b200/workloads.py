@@ -1,0 +1,120 @@
+"""Seeded synthetic inputs of the five benchmark workloads.
+
+The reference's example inputs are ``numpy.random.default_rng(seed)`` draws in
+fp32 followed by a round-to-nearest cast to the storage type
+(``python/intent/examples/programs/inputs.py:16-27, 99-112``); these generators
+keep that order.  No public dataset or benchmark suite is involved: shapes and
+value distributions are the ones the workload descriptions state.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+
+@dataclass(frozen=True)
+class Workload:
+    name: str
+    unit: str              # "GB/s" or "TFLOP/s"
+    bound: str             # "hbm" or "tensor"
+    work: float            # algorithmic bytes (hbm) or flops (tensor) per launch
+    description: str
+
+
+def _f32(array) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(array, dtype=np.float32))
+
+
+def softmax_inputs(m: int = 4096, n: int = 1024, seed: int = 0):
+    rng = np.random.default_rng(seed)
+    return (_f32(rng.standard_normal((m, n), dtype=np.float32)),)
+
+
+def layer_norm_inputs(m: int = 16384, n: int = 4096, seed: int = 0, dtype=torch.float16):
+    rng = np.random.default_rng(seed)
+    x = _f32(rng.standard_normal((m, n), dtype=np.float32)).to(dtype)
+    gamma = _f32(0.5 + rng.random((n,), dtype=np.float32)).to(dtype)
+    beta = _f32(-0.1 + 0.2 * rng.random((n,), dtype=np.float32)).to(dtype)
+    return x, gamma, beta, float(np.float32(1.0 / n)), float(np.float32(1e-5))
+
+
+def gemm_inputs(m: int = 8192, n: int = 8192, k: int = 8192, seed: int = 0, dtype=torch.float16):
+    """A row-major (M,K); B column-major (K,N), i.e. the transpose view of a contiguous (N,K)."""
+    rng = np.random.default_rng(seed)
+    a = _f32(2.0 * rng.random((m, k), dtype=np.float32) - 1.0).to(dtype)
+    bt = _f32(2.0 * rng.random((n, k), dtype=np.float32) - 1.0).to(dtype)
+    return a, bt.t()
+
+
+def attention_inputs(b: int = 8, h: int = 32, s: int = 4096, d: int = 128, seed: int = 0,
+                     dtype=torch.bfloat16, kv_heads: int | None = None):
+    rng = np.random.default_rng(seed)
+    hk = h if kv_heads is None else kv_heads
+    q = _f32(0.5 * rng.standard_normal((b, h, s, d), dtype=np.float32)).to(dtype)
+    k = _f32(0.5 * rng.standard_normal((b, hk, s, d), dtype=np.float32)).to(dtype)
+    v = _f32(0.5 * rng.standard_normal((b, hk, s, d), dtype=np.float32)).to(dtype)
+    return q, k, v, float(np.float32(1.0 / math.sqrt(d)))
+
+
+def csr_inputs(rows: int = 262144, columns: int = 262144, per_row: int = 32, features: int = 128,
+               seed: int = 0):
+    """`per_row` distinct, ascending, uniformly drawn column indices per row."""
+    rng = np.random.default_rng(seed)
+    per_row = min(per_row, columns)
+    column_indices = np.empty((rows, per_row), dtype=np.int32)
+    pending = np.arange(rows)
+    extra = max(8, per_row // 4)
+    while pending.size:
+        if columns <= 4 * per_row:  # dense-ish: exact sampling without replacement
+            block = np.argsort(rng.random((pending.size, columns)), axis=1)[:, :per_row]
+            column_indices[pending] = np.sort(block, axis=1).astype(np.int32)
+            break
+        draw = rng.integers(0, columns, size=(pending.size, per_row + extra), dtype=np.int64)
+        order = np.argsort(draw, axis=1, kind="stable")
+        ranked = np.take_along_axis(draw, order, axis=1)
+        repeated_ranked = np.zeros_like(ranked, dtype=bool)
+        repeated_ranked[:, 1:] = ranked[:, 1:] == ranked[:, :-1]
+        repeated = np.empty_like(repeated_ranked)
+        np.put_along_axis(repeated, order, repeated_ranked, axis=1)  # later occurrences, in draw order
+        enough = (~repeated).sum(axis=1) >= per_row
+        good = np.nonzero(enough)[0]
+        if good.size:
+            # the first per_row distinct draws in draw order (exchangeable, hence uniform), then sorted
+            first = np.argsort(repeated[good], axis=1, kind="stable")[:, :per_row]
+            chosen = np.take_along_axis(draw[good], first, axis=1)
+            column_indices[pending[good]] = np.sort(chosen, axis=1).astype(np.int32)
+        pending = pending[~enough]
+    row_offsets = np.arange(0, rows * per_row + 1, per_row, dtype=np.int32)
+    values = (2.0 * rng.random(rows * per_row, dtype=np.float32) - 1.0).astype(np.float32)
+    dense = rng.standard_normal((columns, features), dtype=np.float32)
+    return (torch.from_numpy(row_offsets), torch.from_numpy(column_indices.reshape(-1)),
+            torch.from_numpy(values), torch.from_numpy(dense))
+
+
+def softmax_workload(m=4096, n=1024) -> Workload:
+    return Workload("softmax", "GB/s", "hbm", 2.0 * m * n * 4, f"row softmax fp32 {m}x{n}")
+
+
+def layer_norm_workload(m=16384, n=4096) -> Workload:
+    return Workload("layer_norm", "GB/s", "hbm", 2.0 * m * n * 2 + 2.0 * n * 2,
+                    f"LayerNorm f16 {m}x{n}, fp32 statistics")
+
+
+def gemm_workload(m=8192, n=8192, k=8192) -> Workload:
+    return Workload("gemm", "TFLOP/s", "tensor", 2.0 * m * n * k,
+                    f"GEMM f16 {m}x{n}x{k}, row-major A, column-major B, fp32 accumulate")
+
+
+def attention_workload(b=8, h=32, s=4096, d=128) -> Workload:
+    return Workload("attention", "TFLOP/s", "tensor", 4.0 * b * h * d * s * (s + 1) / 2,
+                    f"causal flash-attention bf16 B={b} H={h} S={s} D={d}")
+
+
+def spmm_workload(rows=262144, columns=262144, per_row=32, features=128) -> Workload:
+    nnz = rows * per_row
+    compulsory = (rows + 1) * 4 + nnz * 8 + columns * features * 4 + rows * features * 4
+    return Workload("spmm", "GB/s", "hbm", float(compulsory),
+                    f"CSR SpMM fp32 {rows}x{columns}, {per_row} nnz/row, X {columns}x{features}")

@@ -1,0 +1,111 @@
+"""The CPU oracle against float64 restatements of the same kernel definitions and
+against the committed vectors (tests/golden/oracle_vectors.pt).  The reference
+holds no golden vectors for these operators; parity is unpinned."""
+import math
+from pathlib import Path
+
+import pytest
+import torch
+
+import oracle
+from conftest import relative_error
+from intent_b200 import workloads
+
+GOLDEN = Path(__file__).resolve().parent / "golden" / "oracle_vectors.pt"
+
+
+def test_softmax_f32_against_float64():
+    (x,) = workloads.softmax_inputs(64, 1024, seed=3)
+    assert relative_error(oracle.softmax(x), torch.softmax(x.double(), 1)) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_softmax_16bit(dtype):
+    x = torch.randn(9, 257, generator=torch.Generator().manual_seed(1)).to(dtype)
+    assert relative_error(oracle.softmax(x), torch.softmax(x.double(), 1)) <= 1e-2
+
+
+def test_softmax_nan_and_infinities():
+    x = torch.tensor([[1.0, float("nan"), 2.0], [float("-inf"), 0.0, 1.0]])
+    y = oracle.softmax(x)
+    assert torch.isnan(y[0]).all()                     # NaN reaches every output through the sum
+    assert y[1, 0] == 0 and abs(float(y[1].sum()) - 1) < 1e-6
+
+
+def test_layer_norm_against_float64():
+    x, w, b, inv, eps = workloads.layer_norm_inputs(32, 4096, seed=5)
+    expected = torch.nn.functional.layer_norm(x.double(), (4096,), w.double(), b.double(), eps)
+    assert relative_error(oracle.layer_norm(x, w, b, inv, eps), expected) <= 1e-2
+    xf = torch.randn(8, 100, generator=torch.Generator().manual_seed(2))
+    wf, bf = torch.rand(100) + 0.5, torch.rand(100) - 0.5
+    expected = torch.nn.functional.layer_norm(xf.double(), (100,), wf.double(), bf.double(), 1e-5)
+    assert relative_error(oracle.layer_norm(xf, wf, bf, 1 / 100, 1e-5), expected) <= 1e-4
+
+
+def test_gemm_against_float64_and_row_sampling():
+    a, b = workloads.gemm_inputs(96, 130, 200, seed=7)
+    c = oracle.gemm(a, b)
+    assert relative_error(c, a.double() @ b.double()) <= 2e-3
+    part = torch.zeros_like(c)
+    oracle.gemm(a, b, rows=(32, 16), out=part)
+    assert torch.equal(part[32:48], c[32:48]) and not part[:32].any()
+    relu = oracle.gemm(a, b, relu=True)
+    assert torch.equal(relu, torch.clamp_min(c.float(), 0).half()) or relative_error(relu, c.clamp_min(0)) == 0
+
+
+def attention_float64(q, k, v, scale, head_group=1, causal=True):
+    q, k, v = q.double(), k.double(), v.double()
+    k = k.repeat_interleave(head_group, dim=1)
+    v = v.repeat_interleave(head_group, dim=1)
+    s = q @ k.transpose(-1, -2) * scale
+    if causal:
+        mask = torch.arange(q.shape[2])[:, None] >= torch.arange(k.shape[2])[None, :]
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, -1).nan_to_num(0.0)
+    return p @ v
+
+
+@pytest.mark.parametrize("chunk", [16, 64, 128, 10_000])
+def test_attention_against_float64_for_any_slicing(chunk):
+    q, k, v, scale = workloads.attention_inputs(1, 4, 160, 64, seed=11, kv_heads=2)
+    out = oracle.attention(q, k, v, scale, head_group=2, chunk=chunk)
+    assert relative_error(out, attention_float64(q, k, v, scale, 2)) <= 1e-2
+
+
+def test_attention_rows_without_a_valid_key_are_zero():
+    q, k, v, scale = workloads.attention_inputs(1, 1, 8, 64, seed=1)
+    out = oracle.attention(q, k[:, :, :0], v[:, :, :0], scale)
+    assert not out.any()
+    non_causal = oracle.attention(q, k, v, scale, causal=False)
+    assert relative_error(non_causal, attention_float64(q, k, v, scale, causal=False)) <= 1e-2
+
+
+def test_csr_spmm_is_the_sequential_sum_and_validates():
+    ro, ci, va, x = workloads.csr_inputs(200, 300, 17, 24, seed=13)
+    y = oracle.csr_spmm(ro, ci, va, x)
+    expected = torch.zeros(200, 24)
+    for r in range(200):
+        acc = torch.zeros(24)
+        for nz in range(int(ro[r]), int(ro[r + 1])):
+            acc = acc + va[nz] * x[int(ci[nz])]
+        expected[r] = acc
+    assert torch.equal(y, expected)                       # bit-exact: same order, no fused multiply-add
+    oracle.csr_validate(ro, ci, 300)
+    broken = ci.clone()
+    broken[5] = 300
+    with pytest.raises(ValueError):
+        oracle.csr_validate(ro, broken, 300)
+
+
+def test_committed_vectors():
+    vectors = torch.load(GOLDEN)
+    (x,) = workloads.softmax_inputs(4, 16, seed=100)
+    assert torch.equal(oracle.softmax(x), vectors["softmax"])
+    x, w, b, inv, eps = workloads.layer_norm_inputs(4, 64, seed=101)
+    assert torch.equal(oracle.layer_norm(x, w, b, inv, eps), vectors["layer_norm"])
+    a, b = workloads.gemm_inputs(8, 16, 32, seed=102)
+    assert torch.equal(oracle.gemm(a, b), vectors["gemm"])
+    q, k, v, scale = workloads.attention_inputs(1, 2, 32, 64, seed=103)
+    assert torch.equal(oracle.attention(q, k, v, scale, chunk=16), vectors["attention"])
+    ro, ci, va, x = workloads.csr_inputs(8, 32, 4, 16, seed=104)
+    assert torch.equal(oracle.csr_spmm(ro, ci, va, x), vectors["csr_spmm"])
