@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import os
 
-from . import _native
+from . import _native, ops
 from .compilation import (COMPILER, CompilationStageError, CompileOptions, GeneratedProgram, JITKernel,
                   device_capabilities, generate, jit, kernels)
 from .runtime import Artifact, B200Call, B200Program, Interface, register_operator
@@ -42,10 +42,3 @@ def register(*, set_compiler: bool = True) -> None:
     COMPONENTS["b200"] = "intent_b200.provider"
     if set_compiler:
         os.environ.setdefault("INTENT_COMPILER", str(COMPILER))
-
-
-def __getattr__(name):
-    if name == "ops":
-        from . import ops
-        return ops
-    raise AttributeError(name)

@@ -1,0 +1,96 @@
+"""The public API on a device: jit(...).run(), artifact(...) with explicit outputs,
+prepared calls and artifact.as_torch_op(), all through b200-compile + the C ABI."""
+import pytest
+import torch
+
+import intent_b200 as b200
+import oracle
+from conftest import relative_error
+from intent_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_native_library_is_the_one_in_tree():
+    from intent_b200 import _native
+    assert _native.LIBRARY_PATH.exists()
+    _native.library()
+    assert any("libintent_b200.so" in line for line in open("/proc/self/maps"))
+
+
+def test_jit_run_and_explicit_outputs_softmax():
+    (x,) = workloads.softmax_inputs(256, 1024, seed=1)
+    kernel = b200.jit(b200.kernels.stable_softmax)
+    y = kernel.run(x.to(DEV))
+    expected = oracle.softmax(x)
+    assert relative_error(y, expected) <= 1e-5
+    out = torch.empty_like(y)
+    kernel(x.to(DEV), out)                                   # JITKernel.__call__: explicit Out buffer
+    assert torch.equal(out, y)
+    artifact = kernel.artifacts[0]
+    out.zero_()
+    artifact(x.to(DEV), out)                                 # CompiledArtifact.__call__ == launch
+    assert torch.equal(out, y)
+    assert kernel.interface.outputs[0].name == "y"
+    assert artifact.observation.stage == "launched" and artifact.observation.family == "softmax"
+
+
+def test_prepared_call_replays_without_rebinding():
+    x, w, b, inv, eps = workloads.layer_norm_inputs(64, 4096, seed=2)
+    kernel = b200.jit(b200.kernels.layer_norm_f16)
+    xd = x.to(DEV)
+    call = kernel.prepare(xd, w.to(DEV), b.to(DEV), inv, eps)
+    call.compile()
+    call.launch()
+    first = call.result().clone()
+    xd.mul_(2)
+    call.launch()                                            # same bound buffers, new contents
+    assert relative_error(first, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2
+    assert relative_error(call.result(), oracle.layer_norm(x * 2, w, b, inv, eps)) <= 1e-2
+
+
+def test_author_noalias_and_native_requirements():
+    kernel = b200.jit(b200.kernels.stable_softmax)
+    x = torch.randn(8, 64, device=DEV)
+    with pytest.raises(ValueError, match="noalias"):
+        kernel(x, x)
+    kernel_ln = b200.jit(b200.kernels.layer_norm_f16)
+    xh = torch.randn(4, 64, device=DEV).half()
+    w = torch.ones(64, device=DEV).half()
+    with pytest.raises(NotImplementedError, match="nonoverlapping"):
+        kernel_ln(xh, w, w, xh, 1 / 64, 1e-5)
+    with pytest.raises(ValueError, match="executes on cuda"):
+        b200.jit(b200.kernels.stable_softmax, device=0).prepare(torch.randn(2, 2))
+
+
+def test_gemm_and_attention_and_spmm_through_jit():
+    a, bmat = workloads.gemm_inputs(256, 512, 256, seed=3)
+    kernel = b200.jit(b200.kernels.gemm, constexprs={"ACTIVATION": "RELU"})
+    call = kernel.prepare(a.to(DEV), bmat.to(DEV))
+    call.launch()
+    call.check()
+    assert relative_error(call.result(), oracle.gemm(a, bmat, relu=True)) <= 1e-2
+    q, k, v, scale = workloads.attention_inputs(1, 4, 256, 128, seed=4, kv_heads=2)
+    attention = b200.jit(b200.kernels.flash_attention_bf16_fwd, constexprs={"HEAD_GROUP": 2, "CAUSAL": True})
+    out = attention.run(q.to(DEV), k.to(DEV), v.to(DEV), scale)
+    assert relative_error(out, oracle.attention(q, k, v, scale, head_group=2)) <= 1e-2
+    ro, ci, va, x = workloads.csr_inputs(8192, 8192, 32, 128, seed=5)
+    spmm = b200.jit(b200.kernels.csr_spmm)
+    y = spmm.run(ro.to(DEV), ci.to(DEV), va.to(DEV), x.to(DEV))
+    assert torch.equal(y.cpu(), oracle.csr_spmm(ro, ci, va, x))
+
+
+def test_as_torch_op_eager_and_compiled():
+    (x,) = workloads.softmax_inputs(128, 512, seed=6)
+    kernel = b200.jit(b200.kernels.stable_softmax)
+    kernel.prepare(x.to(DEV))
+    op = kernel.as_torch_op("b200_test::softmax_gpu")
+    y = op(x.to(DEV))
+    assert relative_error(y, oracle.softmax(x)) <= 1e-5
+
+    @torch.compile(fullgraph=True)
+    def twice(t):
+        return op(t) * 2
+
+    assert relative_error(twice(x.to(DEV)), oracle.softmax(x) * 2) <= 1e-5

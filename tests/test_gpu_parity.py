@@ -1,0 +1,174 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI, on seeded
+inputs at sizes the oracle finishes in seconds.  Tolerances are the stated ones:
+fp32 softmax rel <= 1e-5; fp32-accumulated GEMM <= 2e-3 before the narrowing cast
+(<= 1e-2 on the f16/bf16 output); 16-bit outputs <= 1e-2; CSR SpMM bit-exact."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from conftest import relative_error
+from intent_b200 import ops, workloads
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def cuda(*tensors):
+    return [t.to(DEV) if isinstance(t, torch.Tensor) else t for t in tensors]
+
+
+# ------------------------------------------------------------------ softmax
+@pytest.mark.parametrize("m,n", [(4096, 1024), (37, 1000), (5, 7), (1, 1), (3, 4097), (2, 40000), (8, 65536),
+                                 (130, 20), (16, 2048)])
+def test_softmax_f32(m, n):
+    (x,) = workloads.softmax_inputs(m, n, seed=m + n)
+    y = ops.softmax(x.to(DEV))
+    assert relative_error(y, oracle.softmax(x)) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n", [(64, 1024), (7, 333), (4, 8200)])
+def test_softmax_16bit(dtype, m, n):
+    x = workloads.softmax_inputs(m, n, seed=1)[0].to(dtype)
+    assert relative_error(ops.softmax(x.to(DEV)), oracle.softmax(x)) <= 1e-2
+
+
+def test_softmax_row_pitch_and_edge_values():
+    (x,) = workloads.softmax_inputs(33, 1100, seed=2)
+    xd = x.to(DEV)
+    view, out = xd[:, 12:1036], torch.zeros(33, 2048, device=DEV)
+    ops.softmax(view, out=out[:, 512:1536])                     # free row pitch, offset base
+    assert relative_error(out[:, 512:1536], oracle.softmax(x[:, 12:1036].contiguous())) <= 1e-5
+    assert not out[:, :512].any() and not out[:, 1536:].any()
+    special = torch.tensor([[1.0, float("nan"), 2.0, 0.0], [float("-inf"), 0.0, 1.0, -1.0]])
+    y = ops.softmax(special.to(DEV)).cpu()
+    assert torch.isnan(y[0]).all() and y[1, 0] == 0
+    assert ops.softmax(torch.empty(0, 8, device=DEV)).shape == (0, 8)
+    with pytest.raises(NotImplementedError):
+        ops.softmax(xd.t())                                        # inner stride != 1
+    with pytest.raises(ValueError):
+        ops.softmax(xd, out=torch.empty(3, 3, device=DEV))
+
+
+# --------------------------------------------------------------- layer norm
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n", [(512, 4096), (33, 1000), (7, 8), (3, 50000), (5, 1001), (64, 16384)])
+def test_layer_norm_16bit(dtype, m, n):
+    x, w, b, inv, eps = workloads.layer_norm_inputs(m, n, seed=n, dtype=dtype)
+    y = ops.layer_norm(*cuda(x, w, b), inv, eps)
+    assert relative_error(y, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2
+
+
+@pytest.mark.parametrize("m,n", [(64, 1024), (9, 100), (4, 40000)])
+def test_weighted_layer_norm_f32(m, n):
+    x, w, b, inv, eps = workloads.layer_norm_inputs(m, n, seed=3, dtype=torch.float32)
+    y = ops.layer_norm(*cuda(x, w, b), inv, eps)
+    assert relative_error(y, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-4
+
+
+def test_layer_norm_strided_parameters():
+    x, w, b, inv, eps = workloads.layer_norm_inputs(17, 512, seed=4)
+    wide_w, wide_b = torch.zeros(512, 2, dtype=w.dtype), torch.zeros(512, 2, dtype=b.dtype)
+    wide_w[:, 0], wide_b[:, 0] = w, b
+    y = ops.layer_norm(x.to(DEV), wide_w.to(DEV)[:, 0], wide_b.to(DEV)[:, 0], inv, eps)
+    assert relative_error(y, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2
+
+
+# --------------------------------------------------------------------- gemm
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 128), (100, 200, 72), (1, 8, 8), (300, 520, 1000),
+                                   (1024, 1024, 1024), (129, 257, 65 * 8), (640, 128, 4096)])
+def test_gemm(dtype, m, n, k):
+    a, b = workloads.gemm_inputs(m, n, k, seed=m + k, dtype=dtype)
+    c = ops.gemm(*cuda(a, b))
+    ops.workspace_status(DEV)
+    expected = oracle.gemm(a, b)
+    assert relative_error(c, expected) <= 1e-2
+    # the f32 accumulators agree to 2e-3 wherever the narrowing cast did not land on a tie
+    assert (c.cpu() == expected).float().mean() > 0.98
+
+
+def test_gemm_relu_empty_k_and_layout_errors():
+    a, b = workloads.gemm_inputs(130, 96, 256, seed=9)
+    c = ops.gemm(*cuda(a, b), relu=True)
+    assert relative_error(c, oracle.gemm(a, b, relu=True)) <= 1e-2 and (c >= 0).all()
+    empty = ops.gemm(torch.empty(8, 0, dtype=torch.float16, device=DEV),
+                     torch.empty(0, 16, dtype=torch.float16, device=DEV))
+    assert empty.shape == (8, 16) and not empty.any()
+    with pytest.raises(NotImplementedError):
+        ops.gemm(a.to(DEV), b.contiguous().to(DEV))                # N-major B is not accepted
+    with pytest.raises(ValueError):
+        ops.gemm(a.to(DEV), b[:-8].to(DEV))
+
+
+def test_gemm_is_linear_in_a():
+    a, b = workloads.gemm_inputs(256, 256, 512, seed=5)
+    ad, bd = cuda(a, b)
+    c1 = ops.gemm(ad, bd).float()
+    c2 = ops.gemm((ad * 2).contiguous(), bd).float()               # scaling by 2 is exact in f16
+    assert torch.equal(c2, c1 * 2)
+
+
+# ---------------------------------------------------------------- attention
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,h,s,d", [(1, 2, 256, 128), (2, 3, 300, 128), (1, 1, 128, 128), (1, 2, 1000, 128),
+                                     (1, 1, 17, 128), (1, 2, 384, 64)])
+def test_flash_attention_causal(dtype, b, h, s, d):
+    q, k, v, scale = workloads.attention_inputs(b, h, s, d, seed=s, dtype=dtype)
+    out = ops.flash_attention(*cuda(q, k, v), scale)
+    ops.workspace_status(DEV)
+    assert relative_error(out, oracle.attention(q, k, v, scale)) <= 1e-2
+
+
+def test_flash_attention_gqa_noncausal_and_rectangular():
+    q, k, v, scale = workloads.attention_inputs(2, 8, 200, 128, seed=21, kv_heads=2)
+    out = ops.flash_attention(*cuda(q, k, v), scale, head_group=4)
+    assert relative_error(out, oracle.attention(q, k, v, scale, head_group=4)) <= 1e-2
+    out = ops.flash_attention(*cuda(q, k, v), scale, head_group=4, causal=False)
+    assert relative_error(out, oracle.attention(q, k, v, scale, head_group=4, causal=False)) <= 1e-2
+    # more queries than keys: rows past the last key see every key; fewer queries than keys
+    short = ops.flash_attention(*cuda(q, k[:, :, :77], v[:, :, :77]), scale, head_group=4)
+    assert relative_error(short, oracle.attention(q, k[:, :, :77].contiguous(), v[:, :, :77].contiguous(),
+                                                  scale, head_group=4)) <= 1e-2
+    few = ops.flash_attention(*cuda(q[:, :, :50], k, v), scale, head_group=4)
+    assert relative_error(few, oracle.attention(q[:, :, :50].contiguous(), k, v, scale, head_group=4)) <= 1e-2
+    ops.workspace_status(DEV)
+
+
+def test_flash_attention_strided_heads():
+    """(B, S, H, D) storage viewed as (B, H, S, D): only the innermost stride must be 1."""
+    q, k, v, scale = workloads.attention_inputs(1, 4, 192, 128, seed=23)
+    packed = [t.permute(0, 2, 1, 3).contiguous().to(DEV).permute(0, 2, 1, 3) for t in (q, k, v)]
+    out = ops.flash_attention(*packed, scale)
+    assert relative_error(out, oracle.attention(q, k, v, scale)) <= 1e-2
+
+
+# --------------------------------------------------------------------- spmm
+@pytest.mark.parametrize("rows,columns,per_row,features", [(1024, 1024, 32, 128), (100, 50, 32, 32), (64, 64, 9, 130),
+                                                           (64, 64, 5, 7), (2048, 4096, 32, 256), (1, 1, 1, 1),
+                                                           (4096, 300, 33, 128)])
+def test_csr_spmm_bit_exact(rows, columns, per_row, features):
+    ro, ci, va, x = workloads.csr_inputs(rows, columns, per_row, features, seed=rows)
+    y = ops.csr_spmm(*cuda(ro, ci, va, x))
+    assert torch.equal(y.cpu(), oracle.csr_spmm(ro, ci, va, x))
+    ops.csr_validate(ro.to(DEV), ci.to(DEV), columns)
+
+
+def test_csr_spmm_ragged_rows_and_validation():
+    ro = torch.tensor([0, 0, 3, 3, 40, 41, 41], dtype=torch.int32)
+    g = torch.Generator().manual_seed(5)
+    ci = torch.randint(0, 64, (41,), dtype=torch.int32, generator=g)   # unsorted, repeated columns are legal
+    va, x = torch.randn(41, generator=g), torch.randn(64, 128, generator=g)
+    y = ops.csr_spmm(*cuda(ro, ci, va, x))
+    assert torch.equal(y.cpu(), oracle.csr_spmm(ro, ci, va, x))
+    assert not y[0].any() and not y[2].any() and not y[5].any()        # empty rows give zeros
+    bad = ci.clone()
+    bad[5] = 64
+    with pytest.raises(ValueError, match="column_indices"):
+        ops.csr_validate(ro.to(DEV), bad.to(DEV), 64)
+    bad_offsets = ro.clone()
+    bad_offsets[3] = 50
+    with pytest.raises(ValueError, match="row_offsets"):
+        ops.csr_validate(bad_offsets.to(DEV), ci.to(DEV), 64)
