@@ -1,0 +1,528 @@
+#!/usr/bin/env python
+"""Benchmark of the b200 operator hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--op NAME|all] [--impl b200|reference]
+
+One JSON line on stdout.  A "step" is one launch of the operator over one
+batch of seeded synthetic input (``intent_b200.workloads``).  The headline
+workload is the LayerNorm configuration (f16 16384 x 4096, 268 MB per step, larger
+than L2); ``--op all`` (the default) also measures softmax, GEMM, attention and
+CSR SpMM and reports them under ``"ops"``.
+
+  value     device-resident throughput: inputs already in HBM, K launches timed with
+            CUDA events on the launching stream between two barriers + syncs,
+            max over ranks, whole-job aggregate (weak scaling: each rank runs the
+            full per-GPU workload, no data-path collective).
+  e2e       the same metric through the public API (jit(...).prepare(...).launch())
+            with HOST buffers: pinned host -> device copy of the step's inputs and a
+            device -> host read of its output inside the timed region.
+  roofline  achieved = algorithmic bytes (or flops) per launch / average launch time,
+            against the pod-measured peak in MEASURED_PEAKS.json.
+  cpu_baseline  the CPU oracle (a port of the reference's kernel definitions; the
+            reference's own compiler and CPU provider cannot be built here) timed on
+            this host's cores with the reference's protocol.
+
+``--impl reference`` times that CPU path alone with every host thread.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
+# summarised under profiles/ (null where no capture of that kernel exists yet).
+NCU_TRAFFIC_BYTES = {"softmax": None, "layer_norm": None, "gemm": None, "attention": None, "spmm": None}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return FALLBACK_PEAKS, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index, self.samples, self.process = device_index, [], None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) >= 9:
+                self.samples.append(fields)
+
+    def __exit__(self, *_):
+        if self.process:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self) -> dict:
+        clocks, reasons, maximum = [], set(), None
+        for fields in self.samples:
+            try:
+                clocks.append(float(fields[1]))
+                maximum = float(fields[2])
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   fields[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in clocks if maximum is None or c > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": maximum,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# --------------------------------------------------------------------------- operators
+class Case:
+    """One operator on one device: resident launch, end-to-end launch, CPU sample."""
+
+    name = ""
+
+    def __init__(self, device):
+        from intent_b200 import workloads
+        self.device = device
+        self.workloads = workloads
+
+    def rotate(self, step: int):
+        """Hook for cases whose working set is smaller than L2: pick a buffer set."""
+
+    def launch(self, step: int) -> None:
+        raise NotImplementedError
+
+    def e2e(self, step: int) -> None:
+        raise NotImplementedError
+
+
+def pinned(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor.contiguous().pin_memory()
+
+
+class SoftmaxCase(Case):
+    name = "softmax"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.softmax_workload()
+        (self.host_x,) = self.workloads.softmax_inputs()
+        # 32 MB per launch fits L2 (126 MB): rotate over 12 buffer pairs (384 MB) so DRAM is measured
+        self.sets = [(self.host_x.to(device) + 0, torch.empty(4096, 1024, device=device)) for _ in range(12)]
+        self.flush = "rotating 12 buffer pairs (384 MB > L2)"
+        self.kernel = b200.jit(b200.kernels.stable_softmax)
+        self.host_in, self.host_out = pinned(self.host_x), torch.empty(4096, 1024).pin_memory()
+        self.dev_in = torch.empty(4096, 1024, device=device)
+        self.call = self.kernel.prepare(self.dev_in)
+        self.h2d, self.d2h = self.host_in.numel() * 4, self.host_out.numel() * 4
+
+    def launch(self, step):
+        x, y = self.sets[step % len(self.sets)]
+        self.ops.softmax(x, out=y)
+
+    def e2e(self, step):
+        self.dev_in.copy_(self.host_in, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        return lambda: oracle.softmax(self.host_x, workers=workers), 1.0, "full workload (4096 rows)"
+
+
+class LayerNormCase(Case):
+    name = "layer_norm"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.layer_norm_workload()
+        self.host = self.workloads.layer_norm_inputs()
+        x, w, b, self.inv, self.eps = self.host
+        self.x, self.w, self.b = x.to(device), w.to(device), b.to(device)
+        self.y = torch.empty_like(self.x)
+        self.flush = "inputs larger than L2 (268 MB per launch vs 126 MB)"
+        self.kernel = b200.jit(b200.kernels.layer_norm_f16)
+        self.host_in, self.host_out = pinned(x), torch.empty_like(x).pin_memory()
+        self.dev_in = torch.empty_like(self.x)
+        self.call = self.kernel.prepare(self.dev_in, self.w, self.b, self.inv, self.eps)
+        self.h2d, self.d2h = x.numel() * 2, x.numel() * 2
+
+    def launch(self, step):
+        self.ops.layer_norm(self.x, self.w, self.b, self.inv, self.eps, out=self.y)
+
+    def e2e(self, step):
+        self.dev_in.copy_(self.host_in, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        x, w, b, inv, eps = self.host
+        return lambda: oracle.layer_norm(x, w, b, inv, eps, workers=workers), 1.0, "full workload (16384 rows)"
+
+
+class GemmCase(Case):
+    name = "gemm"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.gemm_workload()
+        a, b = self.workloads.gemm_inputs()
+        self.host_a, self.host_b = a, b
+        self.a, self.b = a.to(device), b.t().contiguous().to(device).t()
+        self.c = torch.empty(8192, 8192, dtype=torch.float16, device=device)
+        self.flush = "inputs larger than L2 (403 MB per launch vs 126 MB)"
+        self.kernel = b200.jit(b200.kernels.gemm, constexprs={"ACTIVATION": "NONE"})
+        self.host_in_a, self.host_in_b = pinned(a), pinned(b.t())
+        self.dev_a = torch.empty_like(self.a)
+        self.dev_bt = torch.empty(8192, 8192, dtype=torch.float16, device=device)
+        self.host_out = torch.empty(8192, 8192, dtype=torch.float16).pin_memory()
+        self.call = self.kernel.prepare(self.dev_a, self.dev_bt.t())
+        self.h2d, self.d2h = 2 * 8192 * 8192 * 2, 8192 * 8192 * 2
+
+    def launch(self, step):
+        self.ops.gemm(self.a, self.b, out=self.c)
+
+    def e2e(self, step):
+        self.dev_a.copy_(self.host_in_a, non_blocking=True)
+        self.dev_bt.copy_(self.host_in_b, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        rows = 64
+        out = torch.empty(8192, 8192, dtype=torch.float16)
+        return (lambda: oracle.gemm(self.host_a, self.host_b, rows=(0, rows), out=out, workers=workers),
+                rows / 8192, f"{rows} of 8192 rows of C (full K and N)")
+
+
+class AttentionCase(Case):
+    name = "attention"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.attention_workload()
+        q, k, v, self.scale = self.workloads.attention_inputs()
+        self.host = (q, k, v)
+        self.q, self.k, self.v = q.to(device), k.to(device), v.to(device)
+        self.o = torch.empty_like(self.q)
+        self.flush = "inputs larger than L2 (1074 MB per launch vs 126 MB)"
+        self.kernel = b200.jit(b200.kernels.flash_attention_bf16_fwd, constexprs={"HEAD_GROUP": 1, "CAUSAL": True})
+        self.host_in = [pinned(t) for t in (q, k, v)]
+        self.dev_in = [torch.empty_like(self.q) for _ in range(3)]
+        self.host_out = torch.empty_like(q).pin_memory()
+        self.call = self.kernel.prepare(*self.dev_in, self.scale)
+        self.h2d, self.d2h = 3 * q.numel() * 2, q.numel() * 2
+
+    def launch(self, step):
+        self.ops.flash_attention(self.q, self.k, self.v, self.scale, out=self.o)
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        q, k, v = self.host
+        units = max(1, workers)
+        out = torch.empty_like(q)
+        return (lambda: oracle.attention(q, k, v, self.scale, units=(0, units), out=out, workers=workers),
+                units / 256, f"{units} of 256 (batch, head) units, full sequence")
+
+
+class SpmmCase(Case):
+    name = "spmm"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.spmm_workload()
+        self.host = self.workloads.csr_inputs()
+        self.dev = [t.to(device) for t in self.host]
+        self.y = torch.empty(262144, 128, device=device)
+        self.flush = "inputs larger than L2 (337 MB compulsory per launch vs 126 MB)"
+        self.kernel = b200.jit(b200.kernels.csr_spmm_262144)
+        self.host_in = [pinned(t) for t in self.host]
+        self.dev_in = [torch.empty_like(t) for t in self.dev]
+        self.host_out = torch.empty(262144, 128).pin_memory()
+        self.call = self.kernel.prepare(*self.dev_in)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.d2h = self.host_out.numel() * 4
+
+    def launch(self, step):
+        self.ops.csr_spmm(*self.dev, out=self.y)
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        return lambda: oracle.csr_spmm(*self.host, workers=workers), 1.0, "full workload (262144 rows)"
+
+
+CASES = {"softmax": SoftmaxCase, "layer_norm": LayerNormCase, "gemm": GemmCase, "attention": AttentionCase,
+         "spmm": SpmmCase}
+
+
+# --------------------------------------------------------------------------- timing
+def barrier(distributed: bool) -> None:
+    if distributed:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, distributed: bool, device) -> float:
+    if not distributed:
+        return value
+    tensor = torch.tensor([value], dtype=torch.float64, device=device)
+    torch.distributed.all_reduce(tensor, op=torch.distributed.ReduceOp.MAX)
+    return float(tensor.item())
+
+
+def timed(function, steps: int, warmup: int, distributed: bool, device) -> float:
+    """Milliseconds per step: CUDA events on the current (launching) stream, max over ranks."""
+    for step in range(warmup):
+        function(step)
+    barrier(distributed)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for step in range(steps):
+        function(warmup + step)
+    stop.record()
+    barrier(distributed)
+    return max_over_ranks(start.elapsed_time(stop), distributed, device) / steps
+
+
+def timed_graph(function, steps: int, warmup: int, distributed: bool, device) -> float:
+    """Like `timed`, with the K launches captured once in a CUDA graph and replayed, so the
+    device time of short kernels is not hidden behind Python's launch cost (the reference's
+    own tuner times graph replays, python/intent/runtime/triton/cuda.py:18-43)."""
+    for step in range(warmup):
+        function(step)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for step in range(steps):
+            function(warmup + step)
+    graph.replay()
+    barrier(distributed)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    stop.record()
+    barrier(distributed)
+    return max_over_ranks(start.elapsed_time(stop), distributed, device) / steps
+
+
+def cpu_baseline(case, workers: int) -> dict:
+    """Reference CPU timing protocol (python/intent/runtime/mojo/program.py:28-34): evict a
+    64 MiB buffer outside the interval, repetitions = min(50, max(1, int(10 ms / first))),
+    median of 7 samples (fewer when one run is long), scaled from the sample to the workload."""
+    import oracle
+    function, fraction, sample = case.cpu(oracle, workers)
+    eviction = torch.empty(64 * 1024 * 1024, dtype=torch.uint8)
+
+    def once() -> float:
+        oracle.evict(eviction)
+        begin = oracle.now_ms()
+        function()
+        return oracle.now_ms() - begin
+
+    first = once()
+    repetitions = min(50, max(1, int(10.0 / first)))
+    samples = 7 if first < 1500 else 3 if first < 8000 else 1
+    measurements = []
+    for _ in range(samples):
+        measurements.append(sum(once() for _ in range(repetitions)) / repetitions)
+    milliseconds = statistics.median(measurements)
+    work = case.workload.work * fraction
+    scale = 1e6 if case.workload.unit == "GB/s" else 1e9
+    return {"value": work / milliseconds / scale, "unit": case.workload.unit, "cores": workers, "kind": "port",
+            "sample": f"{sample}; median of {samples} x {repetitions} runs, 64 MiB eviction outside the interval",
+            "ms": milliseconds}
+
+
+def measure(case, steps: int, warmup: int, distributed: bool, world: int, peak_table: dict, peak_kind: str,
+            with_cpu: bool) -> dict:
+    workload = case.workload
+    scale = 1e6 if workload.unit == "GB/s" else 1e9      # bytes/ms -> GB/s, flop/ms -> TFLOP/s
+    resident_ms = timed_graph(case.launch, steps, warmup, distributed, case.device)
+    e2e_ms = timed(case.e2e, max(2, steps // 4), 1, distributed, case.device)
+    per_gpu = workload.work / resident_ms / scale
+    if workload.bound == "hbm":
+        peak, peak_name = peak_table["hbm_gbs"], f"{peak_kind} STREAM-style copy"
+    else:
+        peak, peak_name = peak_table["bf16_tflops"], f"{peak_kind} cuBLAS bf16 burst"
+    result = {
+        "op": case.name, "workload": workload.description, "unit": workload.unit,
+        "value": per_gpu * world, "ms_per_step": resident_ms,
+        "e2e": {"value": workload.work / e2e_ms / scale * world, "unit": workload.unit, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": case.h2d, "d2h_bytes_per_step": case.d2h},
+        "roofline": {"bound": workload.bound, "achieved": per_gpu, "peak": peak, "unit": workload.unit,
+                     "frac": per_gpu / peak, "peak_source": peak_name,
+                     "frac_of_nominal": per_gpu / NOMINAL[workload.bound],
+                     "traffic": NCU_TRAFFIC_BYTES[case.name], "algorithmic": workload.work},
+        "l2": case.flush,
+    }
+    if with_cpu:
+        import oracle
+        result["cpu_baseline"] = cpu_baseline(case, oracle.default_workers())
+    return result
+
+
+def run_reference(arguments, rank: int) -> None:
+    """The reference's CPU implementation of the path (the oracle port: the reference
+    itself cannot be compiled here) on every host thread; rank 0 only."""
+    if rank != 0:
+        return
+    import oracle
+    from intent_b200 import workloads
+
+    class HostCase:
+        workload = workloads.layer_norm_workload()
+
+        def __init__(self):
+            self.host = workloads.layer_norm_inputs()
+
+        def cpu(self, module, workers):
+            x, w, b, inv, eps = self.host
+            return lambda: module.layer_norm(x, w, b, inv, eps, workers=workers), 1.0, "full workload (16384 rows)"
+
+    workers = len(os.sched_getaffinity(0))
+    case = HostCase()
+    function, _, sample = case.cpu(oracle, workers)
+    for _ in range(arguments.warmup):
+        function()
+    begin = time.perf_counter()
+    for _ in range(arguments.steps):
+        function()
+    milliseconds = (time.perf_counter() - begin) * 1e3 / arguments.steps
+    value = case.workload.work / milliseconds / 1e6
+    print(json.dumps({
+        "impl": "reference", "metric": "LayerNorm f16 forward throughput (algorithmic bytes / time)",
+        "value": value, "unit": "GB/s", "n_gpus": arguments.gpus, "steps": arguments.steps,
+        "warmup": arguments.warmup, "ms_per_step": milliseconds, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": case.workload.description, "host_threads": workers},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": workers, "kind": "port",
+                         "sample": f"{sample}, {arguments.steps} timed passes"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--op", default="all", choices=["all", *CASES])
+    arguments = parser.parse_args()
+    arguments.warmup = max(arguments.warmup, 3) if arguments.impl == "b200" else arguments.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if arguments.impl == "reference":
+        run_reference(arguments, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: intent_b200 has no CPU execution path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    from intent_b200 import _native
+    _native.library()                                     # fail loudly if the CUDA extension is missing
+    peak_table, peak_kind = peaks()
+    names = list(CASES) if arguments.op == "all" else [arguments.op]
+    primary = "layer_norm" if arguments.op == "all" else arguments.op
+    names.sort(key=lambda name: name != primary)           # the headline workload runs first
+    results, launches = {}, 0
+    with ClockSampler(local_rank) as clocks:
+        for name in names:
+            steps = arguments.steps
+            try:
+                case = CASES[name](device)
+                results[name] = measure(case, steps, arguments.warmup, distributed, world, peak_table, peak_kind,
+                                        with_cpu=(rank == 0 and world == 1))
+                # warm-up + the captured pass + two replays, then the end-to-end warm-up and steps
+                launches += arguments.warmup + 3 * steps + 1 + max(2, steps // 4)
+                del case
+            except Exception as error:  # one failing operator must not hide the others
+                if name == primary:
+                    raise
+                results[name] = {"op": name, "error": f"{type(error).__name__}: {error}"}
+            torch.cuda.empty_cache()
+    clock_summary = clocks.summary()
+    if distributed:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    if rank != 0:
+        return
+    head = results[primary]
+    line = {
+        "metric": f"{head['op']} throughput (algorithmic {'bytes' if head['unit'] == 'GB/s' else 'flops'} / time)",
+        "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": arguments.steps,
+        "warmup": arguments.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": {"softmax": "f32", "layer_norm": "f16", "gemm": "f16", "attention": "bf16", "spmm": "f32"}[primary],
+        "data": "synthetic",
+        "config": {"workload": head["workload"], "l2": head["l2"],
+                   "parallelism": f"{world} independent shard(s), no data-path collective"},
+        "roofline": head["roofline"], "e2e": head["e2e"], "gpu_launches": launches, "clocks": clock_summary,
+        "ops": [results[name] for name in names],
+    }
+    if "cpu_baseline" in head:
+        line["cpu_baseline"] = head["cpu_baseline"]
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()
