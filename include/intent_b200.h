@@ -110,6 +110,42 @@ int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a
               int32_t dtype, int32_t relu, void *stream);
 
 /*
+ * b200_gemm for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference, whose runtime always allocates invocation
+ * workspaces itself (python/intent/runtime/native.py:207-209).
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits — a host
+ * function driven from inside another framework's stream-ordered region, a
+ * real-time or safety-partitioned process whose memory budget is fixed at
+ * start-up, a plugin that is handed device buffers but no allocator.  Such a
+ * caller cannot provide b200_gemm's workspace view.  Here the status words the
+ * kernel's bounded waits use live in a device array that is part of this
+ * library: B200_WORKSPACE_WORDS int32 words (256 bytes), held by every GPU
+ * that loads the library until the process exits.  The call itself makes no
+ * cudaMalloc / cudaFree and no other allocating library call, and keeps no
+ * host-side cache.
+ *
+ * Arguments are b200_gemm's without the workspace view, plus wait_and_check:
+ *   0  enqueue only, like b200_gemm; a device-side timeout goes unreported;
+ *   1  also synchronise `stream` and return B200_ERR_DEVICE_TIMEOUT if a
+ *      bounded wait gave up.
+ * Limits: each of M, N, K at most B200_STATIC_SCRATCH_MAX_EXTENT; larger
+ * problems are refused with B200_ERR_UNSUPPORTED_LAYOUT.  Layout rules are
+ * b200_gemm's.
+ * The first call on a device looks the array's address up (one
+ * cudaGetSymbolAddress with that device current); make that call before any
+ * stream capture begins.  All calls on one GPU share the array: every call
+ * clears the status words on `stream` before its kernel, so calls that
+ * overlap on the GPU (different streams) race on them and may lose or
+ * misattribute a timeout report; results in C are unaffected.
+ */
+#define B200_STATIC_SCRATCH_MAX_EXTENT 2147483647LL
+int b200_gemm_static_scratch(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a_s1,
+                             const void *b, int64_t b_d0, int64_t b_d1, int64_t b_s0, int64_t b_s1,
+                             void *c, int64_t c_d0, int64_t c_d1, int64_t c_s0, int64_t c_s1,
+                             int32_t dtype, int32_t relu, int32_t wait_and_check, void *stream);
+
+/*
  * Flash-attention forward (online softmax over key tiles), bf16 or f16.
  * Replaces flash_attention_bf16_fwd, flash_attention_fwd and
  * flash_gqa_attention_fwd

@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200_softmax": _view(2) + _view(2) + [_I32, _P],
     "b200_layer_norm": _view(2) + _view(1) + _view(1) + _view(2) + [_F32, _F32, _I32, _I32, _P],
     "b200_gemm": _view(2) + _view(2) + _view(2) + _view(1) + [_I32, _I32, _P],
+    "b200_gemm_static_scratch": _view(2) + _view(2) + _view(2) + [_I32, _I32, _I32, _P],
     "b200_flash_attention": _view(4) * 4 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_csr_spmm": _view(1) * 3 + _view(2) * 2 + [_P],
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],

@@ -375,3 +375,119 @@ extern "C" int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0
   return gemm_typed<__nv_bfloat16>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)c, m, n, k,
                                    a_pitch, b_pitch, c_s0, relu, (int *)workspace, s);
 }
+
+// ---------------------------------------------------------------------------
+// b200_gemm_static_scratch: the same GEMM for callers that cannot allocate.
+//
+// The kernel's only scratch is the pair of status words that the bounded waits
+// write when they give up.  Here those words live in a file-scope device array
+// that every GPU loading this library carries until the process exits, so the
+// caller hands over nothing but its operands.
+// ---------------------------------------------------------------------------
+namespace b200 {
+namespace {
+
+// Fixed footprint: kStaticScratchWords int32 words (256 bytes) per GPU.  The
+// kernel uses words 0 and 1 whatever the problem size, so the limit that a call
+// can exceed is the extent limit stated at the entry, not the scratch itself.
+constexpr int kStaticScratchWords = B200_WORKSPACE_WORDS;
+static __device__ __align__(256) int static_scratch[kStaticScratchWords];
+
+// `static_scratch` is only a stand-in for the device symbol in host code; the
+// address a kernel may be given comes from cudaGetSymbolAddress, once per
+// device, with that device current.
+constexpr int kMaxDevices = 64;
+int *static_scratch_address[kMaxDevices];
+std::mutex static_scratch_lock;
+
+int resolve_static_scratch(int **address) {
+  int device = -1;
+  B200_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices)
+    return fail(B200_ERR_DEVICE, "gemm_static_scratch: device ordinal %d is outside [0, %d)", device, kMaxDevices);
+  std::lock_guard<std::mutex> guard(static_scratch_lock);
+  if (!static_scratch_address[device]) {
+    void *pointer = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&pointer, static_scratch));
+    static_scratch_address[device] = static_cast<int *>(pointer);
+  }
+  *address = static_scratch_address[device];
+  return B200_OK;
+}
+
+template <typename T>
+int gemm_static_scratch_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, int64_t a_pitch,
+                              int64_t b_pitch, int64_t c_pitch, int relu, int *status, cudaStream_t stream) {
+  if (k == 0) {
+    zero_fill_kernel<T><<<sm_count() * 4, 256, 0, stream>>>(c, c_pitch, (int)m, (int)n);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  }
+  // Tensor maps are encoded on the stack: no cache, no heap.
+  CUtensorMap map_a, map_b;
+  const uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, dims_b[2] = {(uint64_t)k, (uint64_t)n};
+  const uint64_t stride_a[1] = {(uint64_t)a_pitch * 2}, stride_b[1] = {(uint64_t)b_pitch * 2};
+  const uint32_t box_a[2] = {kBlockK, kBlockM}, box_b[2] = {kBlockK, kBlockN};
+  int result = encode_tensor_map_16bit(&map_a, a, 2, dims_a, stride_a, box_a, true);
+  if (result != B200_OK) return result;
+  result = encode_tensor_map_16bit(&map_b, b, 2, dims_b, stride_b, box_b, true);
+  if (result != B200_OK) return result;
+  auto kernel = relu ? gemm_kernel<T, true> : gemm_kernel<T, false>;
+  B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + kBlockN - 1) / kBlockN);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, c, c_pitch, (int)m, (int)n, (int)k, status);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_gemm_static_scratch(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a_s1,
+                                        const void *b, int64_t b_d0, int64_t b_d1, int64_t b_s0, int64_t b_s1,
+                                        void *c, int64_t c_d0, int64_t c_d1, int64_t c_s0, int64_t c_s1,
+                                        int32_t dtype, int32_t relu, int32_t wait_and_check, void *stream) {
+  const int64_t m = a_d0, k = a_d1, n = b_d1;
+  if (m < 0 || n < 0 || k < 0 || b_d0 != k || c_d0 != m || c_d1 != n)
+    return fail(B200_ERR_INVALID_ARGUMENT, "gemm_static_scratch: a is %lldx%lld, b is %lldx%lld, c is %lldx%lld",
+                (long long)a_d0, (long long)a_d1, (long long)b_d0, (long long)b_d1, (long long)c_d0, (long long)c_d1);
+  if (m > B200_STATIC_SCRATCH_MAX_EXTENT || n > B200_STATIC_SCRATCH_MAX_EXTENT || k > B200_STATIC_SCRATCH_MAX_EXTENT)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT,
+                "gemm_static_scratch: extents %lld x %lld x %lld exceed the supported maximum of %lld per dimension",
+                (long long)m, (long long)n, (long long)k, (long long)B200_STATIC_SCRATCH_MAX_EXTENT);
+  if (m == 0 || n == 0) return B200_OK;
+  if (!c || (k > 0 && (!a || !b))) return fail(B200_ERR_INVALID_ARGUMENT, "gemm_static_scratch: null buffer");
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return fail(B200_ERR_INVALID_ARGUMENT, "gemm_static_scratch: element type %d is not f16/bf16", dtype);
+  if (n > 1 && c_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm_static_scratch: c must be row-major (c_s1 == 1)");
+  if (k > 1 && a_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm_static_scratch: a must be K-major (a_s1 == 1)");
+  if (k > 1 && b_s0 != 1)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm_static_scratch: b must be K-major (b_s0 == 1, column-major (K,N))");
+  const int64_t a_pitch = m > 1 ? a_s0 : (k + 7) / 8 * 8;
+  const int64_t b_pitch = n > 1 ? b_s1 : (k + 7) / 8 * 8;
+  if (k > 0 && (a_pitch % 8 || b_pitch % 8 || a_pitch < k || b_pitch < k || !aligned16(a) || !aligned16(b)))
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT,
+                "gemm_static_scratch: TMA needs 16-byte aligned bases and leading strides that are multiples of 8 "
+                "elements and >= K");
+  int *scratch = nullptr;
+  int result = resolve_static_scratch(&scratch);
+  if (result != B200_OK) return result;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the sticky status words must start at zero.
+  B200_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * sizeof(int), s));
+  if (dtype == B200_F16)
+    result = gemm_static_scratch_typed<__half>((const __half *)a, (const __half *)b, (__half *)c, m, n, k, a_pitch,
+                                               b_pitch, c_s0, relu, scratch, s);
+  else
+    result = gemm_static_scratch_typed<__nv_bfloat16>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b,
+                                                      (__nv_bfloat16 *)c, m, n, k, a_pitch, b_pitch, c_s0, relu,
+                                                      scratch, s);
+  if (result != B200_OK || !wait_and_check) return result;
+  int words[2] = {0, 0};
+  B200_CUDA_TRY(cudaMemcpyAsync(words, scratch, sizeof words, cudaMemcpyDeviceToHost, s));
+  B200_CUDA_TRY(cudaStreamSynchronize(s));
+  if (words[0] != 0)
+    return fail(B200_ERR_DEVICE_TIMEOUT, "gemm_static_scratch: a bounded device-side wait gave up (site %d)", words[1]);
+  return B200_OK;
+}
