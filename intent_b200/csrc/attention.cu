@@ -1,10 +1,407 @@
-// placeholder until the tcgen05 kernel lands
-#include "common.cuh"
+// Flash-attention forward on the tcgen05 tensor cores (bf16 / f16, head dim 128).
+//
+// One CTA owns one tile of 128 query rows of one (batch, head) and streams the
+// key/value sequence through it in tiles of 128 keys.  Two CTAs are resident per
+// SM (256 TMEM columns and ~97 KB of shared memory each), so while one CTA's
+// softmax warps work on a score tile the other CTA's MMAs keep the tensor pipe
+// busy.
+//
+//   warp 0      TMA producer: Q once, then K_j / V_j into two 32 KB slots
+//               (128 rows x 128 B, two 64-column halves, 128-byte swizzle)
+//   warp 1      MMA issuer:  S = Q . K_j^T   (A, B from shared memory, K-major)
+//                            O += P . V_j    (A = P from TMEM, B = V MN-major)
+//   warps 2..5  softmax: thread r owns query row r.  tcgen05.ld the 128 scores,
+//               row maximum, p = ex2.approx.ftz(s*scale*log2e - m), f32 row sum,
+//               P rounded to the operand type and written back over the score
+//               columns (tcgen05.st); the running maximum is only replaced, and O
+//               and the sum rescaled, when it grows by more than 2^8, which keeps
+//               the accumulator exact in the usual online-softmax sense while
+//               rescales stay rare.  Last: O * div.approx.ftz(1, sum) -> global.
+//
+// TMEM: columns [0,128) scores S (P aliases [0,64)), [128,256) accumulator O.
+// Causal tiles that lie entirely above the diagonal are never visited; the
+// diagonal tile and the ragged last key tile are masked element-wise.
+// Work per launch: 4*B*H*D*S*(S+1)/2 flop (causal), 4*B*H*S*D*2 compulsory bytes.
+#include <mutex>
+#include <type_traits>
+
+#include "tc.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kHeadDim = 128;
+constexpr int kThreads = 192;
+constexpr int kTmemColumns = 256;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one Q / K / V tile
+constexpr uint32_t kHalfBytes = kTileBytes / 2;  // 64-column half
+constexpr float kRescaleThreshold = 8.0f;        // log2 units
+
+struct __align__(8) Barriers {
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_ready, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSmemBytes = 1024 + 3 * kTileBytes + sizeof(Barriers);
+
+struct Shape {
+  int batch, heads_q, seq_q, seq_k, head_group, causal;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  float scale_log2;
+};
+
+__device__ __forceinline__ float ex2_approx_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float div_approx_ftz(float a, float b) {
+  float y;
+  asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(y) : "f"(a), "f"(b));
+  return y;
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const Shape shape, int *status) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char *tiles = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+  unsigned char *q_tile = tiles, *k_tile = tiles + kTileBytes, *v_tile = tiles + 2 * kTileBytes;
+  Barriers *bars = reinterpret_cast<Barriers *>(tiles + 3 * kTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest query tiles (most key tiles under the causal mask) are scheduled first
+  const int q_tiles = (shape.seq_q + kBlockM - 1) / kBlockM;
+  const int q_tile_index = q_tiles - 1 - (int)blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / shape.head_group;
+  const int q0 = q_tile_index * kBlockM;
+  int key_tiles = (shape.seq_k + kBlockN - 1) / kBlockN;
+  if (shape.causal) key_tiles = min(key_tiles, (q0 + kBlockM - 1) / kBlockN + 1);
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bars->q_full, 1);
+    tc::mbar_init(&bars->k_full, 1);
+    tc::mbar_init(&bars->k_empty, 1);
+    tc::mbar_init(&bars->v_full, 1);
+    tc::mbar_init(&bars->v_empty, 1);
+    tc::mbar_init(&bars->s_full, 1);
+    tc::mbar_init(&bars->p_ready, 4);
+    tc::mbar_init(&bars->o_full, 1);
+    bars->abort_flag = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_descriptor(&map_q);
+    tc::tma_prefetch_descriptor(&map_k);
+    tc::tma_prefetch_descriptor(&map_v);
+  }
+  if (warp == 1) tc::tmem_alloc(&bars->tmem_base, kTmemColumns);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kBlockN;
+  volatile int *abort_flag = &bars->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (tc::elect_one()) {
+      tc::mbar_expect_tx(&bars->q_full, kTileBytes);
+      tc::tma_load_4d(q_tile, &map_q, &bars->q_full, 0, q0, head, batch);
+      tc::tma_load_4d(q_tile + kHalfBytes, &map_q, &bars->q_full, 64, q0, head, batch);
+      int loaded_k = 0, loaded_v = 0;
+      bool alive = true;
+      for (int j = 0; alive && j < key_tiles; ++j) {
+        const uint32_t phase = j & 1;
+        if (!tc::mbar_wait(&bars->k_empty, phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) { alive = false; break; }
+        tc::mbar_expect_tx(&bars->k_full, kTileBytes);
+        tc::tma_load_4d(k_tile, &map_k, &bars->k_full, 0, j * kBlockN, kv_head, batch);
+        tc::tma_load_4d(k_tile + kHalfBytes, &map_k, &bars->k_full, 64, j * kBlockN, kv_head, batch);
+        ++loaded_k;
+        if (!tc::mbar_wait(&bars->v_empty, phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) { alive = false; break; }
+        tc::mbar_expect_tx(&bars->v_full, kTileBytes);
+        tc::tma_load_4d(v_tile, &map_v, &bars->v_full, 0, j * kBlockN, kv_head, batch);
+        tc::tma_load_4d(v_tile + kHalfBytes, &map_v, &bars->v_full, 64, j * kBlockN, kv_head, batch);
+        ++loaded_v;
+      }
+      if (!alive) {
+        // let copies in flight land before the shared memory goes away
+        const long long start = clock64();
+        while (!tc::mbar_try_wait(&bars->q_full, 0) && clock64() - start < tc::kWaitCycles / 8) {}
+        if (loaded_k) while (!tc::mbar_try_wait(&bars->k_full, (loaded_k - 1) & 1) && clock64() - start < tc::kWaitCycles / 8) {}
+        if (loaded_v) while (!tc::mbar_try_wait(&bars->v_full, (loaded_v - 1) & 1) && clock64() - start < tc::kWaitCycles / 8) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer
+    if (tc::elect_one()) {
+      constexpr int format = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = tc::instr_desc_f16(format, kBlockM, kBlockN, false);
+      constexpr uint32_t idesc_o = tc::instr_desc_f16(format, kBlockM, kHeadDim, true);
+      bool alive = tc::mbar_wait(&bars->q_full, 0, abort_flag, status, tc::kSiteMmaFull);
+      const uint32_t q_address = tc::smem_u32(q_tile), k_address = tc::smem_u32(k_tile), v_address = tc::smem_u32(v_tile);
+      for (int j = 0; alive && j < key_tiles; ++j) {
+        const uint32_t phase = j & 1;
+        if (!tc::mbar_wait(&bars->k_full, phase, abort_flag, status, tc::kSiteMmaFull)) break;
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+          const uint32_t offset = (kk / 4) * kHalfBytes + (kk % 4) * 32;
+          tc::mma_f16_ss(tmem_s, tc::smem_desc_k_major_sw128(q_address + offset),
+                         tc::smem_desc_k_major_sw128(k_address + offset), idesc_s, kk != 0);
+        }
+        tc::mma_commit(&bars->k_empty);
+        tc::mma_commit(&bars->s_full);
+        if (!tc::mbar_wait(&bars->v_full, phase, abort_flag, status, tc::kSiteMmaFull)) break;
+        if (!tc::mbar_wait(&bars->p_ready, phase, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          // A: 16 keys = 8 packed TMEM columns; B: 16 key rows = 2048 bytes further down the V tile
+          tc::mma_f16_ts(tmem_o, tmem_s + kk * 8, tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes),
+                         idesc_o, (j | kk) != 0);
+        }
+        tc::mma_commit(&bars->v_empty);
+        if (j == key_tiles - 1) tc::mma_commit(&bars->o_full);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- softmax
+    const int quadrant = warp & 3;
+    const int row_in_tile = quadrant * 32 + lane;
+    const int q_row = q0 + row_in_tile;
+    const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+    float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
+    float sum = 0.0f;
+    bool alive = true;
+    for (int j = 0; alive && j < key_tiles; ++j) {
+      const uint32_t phase = j & 1;
+      if (!tc::mbar_wait(&bars->s_full, phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
+      tc::tc_fence_after_sync();
+      float s[kBlockN];
+#pragma unroll
+      for (int chunk = 0; chunk < kBlockN / 32; ++chunk) {
+        uint32_t raw[32];
+        tc::tmem_load_32x32(tmem_s + lane_base + chunk * 32, raw);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[chunk * 32 + i] = __uint_as_float(raw[i]);
+      }
+      tc::tmem_load_wait();
+      const int k0 = j * kBlockN;
+      const bool masked_tile = (k0 + kBlockN > shape.seq_k) || (shape.causal && k0 + kBlockN - 1 > q0);
+      if (masked_tile) {
+        const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
+#pragma unroll
+        for (int i = 0; i < kBlockN; ++i)
+          if (i >= limit) s[i] = -INFINITY;
+      }
+      float tile_max = s[0];
+#pragma unroll
+      for (int i = 1; i < kBlockN; ++i) tile_max = fmaxf(tile_max, s[i]);
+      tile_max *= shape.scale_log2;
+      // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
+      const bool grow = tile_max > reference + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = grow ? ex2_approx_ftz(reference - tile_max) : 1.0f;  // 0 on the first tile
+        if (grow) { reference = tile_max; sum *= factor; }
+        if (j > 0) {
+          // S(j) has completed, hence P.V(j-1) too: O is quiescent until p_ready is signalled
+#pragma unroll 1
+          for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
+            uint32_t raw[32];
+            tc::tmem_load_32x32(tmem_o + lane_base + chunk * 32, raw);
+            tc::tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * factor);
+            tc::tmem_store_32x32(tmem_o + lane_base + chunk * 32, raw);
+          }
+        }
+      }
+      const float offset = -reference;
+#pragma unroll
+      for (int chunk = 0; chunk < kBlockN / 64; ++chunk) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i], shape.scale_log2, offset));
+          const float p1 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i + 1], shape.scale_log2, offset));
+          sum += p0 + p1;
+          packed[i] = pack_pair<T>(p0, p1);
+        }
+        tc::tmem_store_32x32(tmem_s + lane_base + chunk * 32, packed);
+      }
+      tc::tmem_store_wait();
+      tc::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&bars->p_ready);
+    }
+    if (alive && tc::mbar_wait(&bars->o_full, 0, abort_flag, status, tc::kSiteEpilogueTmemFull)) {
+      tc::tc_fence_after_sync();
+      const float inverse = div_approx_ftz(1.0f, sum);
+      T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s;
+      const bool vector_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && shape.o_stride_b % 8 == 0 &&
+                             shape.o_stride_h % 8 == 0 && shape.o_stride_s % 8 == 0;
+#pragma unroll 1
+      for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
+        uint32_t raw[32];
+        tc::tmem_load_32x32(tmem_o + lane_base + chunk * 32, raw);
+        tc::tmem_load_wait();
+        if (q_row < shape.seq_q) {
+          if (vector_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              v.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]) * inverse, __uint_as_float(raw[q * 8 + 1]) * inverse);
+              v.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]) * inverse, __uint_as_float(raw[q * 8 + 3]) * inverse);
+              v.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]) * inverse, __uint_as_float(raw[q * 8 + 5]) * inverse);
+              v.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]) * inverse, __uint_as_float(raw[q * 8 + 7]) * inverse);
+              *reinterpret_cast<uint4 *>(destination + chunk * 32 + q * 8) = v;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              destination[chunk * 32 + i] = Element<T>::narrow(__uint_as_float(raw[i]) * inverse);
+          }
+        }
+      }
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemColumns);
+  }
+}
+
+// Rows with no valid key (an empty key sequence) are zero.
+template <typename T>
+__global__ void zero_output_kernel(T *out, int64_t total_rows, int heads, int seq, int dv, int64_t sb, int64_t sh,
+                                   int64_t ss) {
+  const int64_t total = total_rows * dv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / dv, d = i % dv;
+    const int64_t b = row / ((int64_t)heads * seq), h = (row / seq) % heads, s = row % seq;
+    out[b * sb + h * sh + s * ss + d] = Element<T>::narrow(0.0f);
+  }
+}
+
+int tensor_map_4d(CUtensorMap *map, const void *base, int64_t d0, int64_t d1, int64_t d2, int64_t d3, int64_t s0,
+                  int64_t s1, int64_t s2) {
+  // innermost first: (D, S, H, B); a size-1 dimension may carry any stride, give TMA a legal one
+  const uint64_t dims[4] = {(uint64_t)d3, (uint64_t)d2, (uint64_t)d1, (uint64_t)d0};
+  auto legal = [&](int64_t stride, int64_t extent, int64_t fallback) {
+    return (uint64_t)((extent > 1 ? stride : fallback) * 2);
+  };
+  const int64_t row = (d3 + 7) / 8 * 8;
+  const uint64_t strides[3] = {legal(s2, d2, row), legal(s1, d1, row * d2), legal(s0, d0, row * d2 * d1)};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tensor_map_16bit(map, base, 4, dims, strides, box, true);
+}
+
+template <typename T>
+int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd, const int64_t *qs,
+                    const int64_t *kd, const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
+                    int head_group, int causal, int *status, cudaStream_t stream) {
+  const int64_t batch = qd[0], heads_q = qd[1], seq_q = qd[2], heads_k = kd[1], seq_k = kd[2];
+  if (seq_k == 0) {
+    zero_output_kernel<T><<<sm_count() * 4, 256, 0, stream>>>(o, batch * heads_q * seq_q, (int)heads_q, (int)seq_q,
+                                                              kHeadDim, os[0], os[1], os[2]);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  int result = tensor_map_4d(&map_q, q, batch, heads_q, seq_q, kHeadDim, qs[0], qs[1], qs[2]);
+  if (result != B200_OK) return result;
+  result = tensor_map_4d(&map_k, k, batch, heads_k, seq_k, kHeadDim, ks[0], ks[1], ks[2]);
+  if (result != B200_OK) return result;
+  result = tensor_map_4d(&map_v, v, batch, heads_k, seq_k, kHeadDim, vs[0], vs[1], vs[2]);
+  if (result != B200_OK) return result;
+  auto kernel = attention_kernel<T>;
+  static std::once_flag configured;
+  cudaError_t attribute_error = cudaSuccess;
+  std::call_once(configured, [&] {
+    attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  });
+  B200_CUDA_TRY(attribute_error);
+  Shape shape;
+  shape.batch = (int)batch; shape.heads_q = (int)heads_q; shape.seq_q = (int)seq_q; shape.seq_k = (int)seq_k;
+  shape.head_group = head_group; shape.causal = causal;
+  shape.o_stride_b = os[0]; shape.o_stride_h = os[1]; shape.o_stride_s = os[2];
+  shape.scale_log2 = scale * (float)1.4426950408889634;  // scale * LOG2E, rounded to f32 like the kernel definition
+  const dim3 grid((unsigned)((seq_q + kBlockM - 1) / kBlockM), (unsigned)heads_q, (unsigned)batch);
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, o, shape, status);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
 using namespace b200;
-extern "C" int b200_flash_attention(const void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                         const void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                         const void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                         void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                         float, void *, int64_t, int64_t, int32_t, int32_t, int32_t, void *) {
-  return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: not built yet");
+
+extern "C" int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
+                                    int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,
+                                    const void *k, int64_t k_d0, int64_t k_d1, int64_t k_d2, int64_t k_d3,
+                                    int64_t k_s0, int64_t k_s1, int64_t k_s2, int64_t k_s3,
+                                    const void *v, int64_t v_d0, int64_t v_d1, int64_t v_d2, int64_t v_d3,
+                                    int64_t v_s0, int64_t v_s1, int64_t v_s2, int64_t v_s3,
+                                    void *o, int64_t o_d0, int64_t o_d1, int64_t o_d2, int64_t o_d3,
+                                    int64_t o_s0, int64_t o_s1, int64_t o_s2, int64_t o_s3,
+                                    float scale, void *workspace, int64_t ws_d0, int64_t ws_s0,
+                                    int32_t dtype, int32_t head_group, int32_t causal, void *stream) {
+  const int64_t qd[4] = {q_d0, q_d1, q_d2, q_d3}, qs[4] = {q_s0, q_s1, q_s2, q_s3};
+  const int64_t kd[4] = {k_d0, k_d1, k_d2, k_d3}, ks[4] = {k_s0, k_s1, k_s2, k_s3};
+  const int64_t vd[4] = {v_d0, v_d1, v_d2, v_d3}, vs[4] = {v_s0, v_s1, v_s2, v_s3};
+  const int64_t od[4] = {o_d0, o_d1, o_d2, o_d3}, os[4] = {o_s0, o_s1, o_s2, o_s3};
+  for (int i = 0; i < 4; ++i)
+    if (qd[i] < 0 || kd[i] < 0 || vd[i] < 0 || od[i] < 0) return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: negative extent");
+  if (head_group < 1 || kd[0] != qd[0] || vd[0] != qd[0] || od[0] != qd[0] || qd[1] != kd[1] * head_group ||
+      vd[1] != kd[1] || od[1] != qd[1] || vd[2] != kd[2] || od[2] != qd[2] || kd[3] != qd[3] || od[3] != vd[3])
+    return fail(B200_ERR_INVALID_ARGUMENT,
+                "flash_attention: q (B,HQ,Q,D), k (B,HK,K,D), v (B,HK,K,DV), o (B,HQ,Q,DV) with HQ = HK * head_group");
+  if (qd[0] == 0 || qd[1] == 0 || qd[2] == 0) return B200_OK;
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: element type %d is not f16/bf16", dtype);
+  if (qd[3] != kHeadDim || vd[3] != kHeadDim)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: head dimensions must be 128 (got D=%lld, DV=%lld)",
+                (long long)qd[3], (long long)vd[3]);
+  if (!q || !k || !v || !o) return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: null buffer");
+  if (!workspace || ws_d0 < B200_WORKSPACE_WORDS || (ws_d0 > 1 && ws_s0 != 1))
+    return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: workspace must hold %d contiguous int32 words", B200_WORKSPACE_WORDS);
+  if (q_s3 != 1 || k_s3 != 1 || v_s3 != 1 || o_s3 != 1)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: innermost strides must be 1");
+  const void *bases[3] = {q, k, v};
+  const int64_t *strides[3] = {qs, ks, vs};
+  const int64_t *extents[3] = {qd, kd, vd};
+  for (int t = 0; t < 3; ++t) {
+    if (!aligned16(bases[t])) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: TMA needs 16-byte aligned bases");
+    for (int axis = 0; axis < 3; ++axis)
+      if (extents[t][axis] > 1 && (strides[t][axis] % 8 || strides[t][axis] <= 0))
+        return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: outer strides must be positive multiples of 8 elements");
+  }
+  if (qd[2] > INT32_MAX - 256 || kd[2] > INT32_MAX - 256 || qd[1] > 65535 || qd[0] > 65535)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: extent exceeds the launch limits");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_F16)
+    return attention_typed<__half>((const __half *)q, (const __half *)k, (const __half *)v, (__half *)o, qd, qs, kd, ks,
+                                   vs, os, scale, head_group, causal, (int *)workspace, s);
+  return attention_typed<__nv_bfloat16>((const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v,
+                                        (__nv_bfloat16 *)o, qd, qs, kd, ks, vs, os, scale, head_group, causal,
+                                        (int *)workspace, s);
 }

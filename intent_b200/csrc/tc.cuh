@@ -107,6 +107,13 @@ __device__ __forceinline__ void tma_load_3d(void *smem, const CUtensorMap *map, 
       ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void *smem, const CUtensorMap *map, uint64_t *bar, int x, int y, int z,
+                                            int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 // 2-D tiled store from shared memory (bulk async group).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smem, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -162,12 +169,29 @@ __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addres
   return desc;
 }
 
+// Shared-memory descriptor of an MN-major operand (the contiguous direction is
+// M or N, not K) made of TMA boxes of [64 elements x rows] with 128-byte
+// swizzle: inside a box, consecutive K rows are 128 bytes apart and groups of 8
+// rows 1024 bytes apart (stride byte offset); boxes that continue the MN
+// direction are `mn_chunk_bytes` apart (leading byte offset).  Stepping K by 16
+// rows adds 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t smem_address, uint32_t mn_chunk_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4);
+  desc |= static_cast<uint64_t>((mn_chunk_bytes & 0x3ffffu) >> 4) << 16;  // leading byte offset
+  desc |= static_cast<uint64_t>(1024u >> 4) << 32;                        // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
 // Instruction descriptor of tcgen05.mma.kind::f16: f32 accumulate, both
 // operands K-major, no negation / sparsity / saturation.
 // format: 0 = f16, 1 = bf16.
-__host__ __device__ constexpr uint32_t instr_desc_f16(int format, int m, int n) {
+__host__ __device__ constexpr uint32_t instr_desc_f16(int format, int m, int n, bool b_mn_major = false) {
   return (1u << 4) | (static_cast<uint32_t>(format) << 7) | (static_cast<uint32_t>(format) << 10) |
-         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+         (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] . B[smem]; one thread issues for the CTA.
