@@ -154,7 +154,8 @@ int b200_gemm_static_scratch(const void *a, int64_t a_d0, int64_t a_d1, int64_t 
  * query head / head_group.  exp2 and the final reciprocal use
  * ex2.approx.ftz / div.approx.ftz as the reference's NVIDIA target does
  * (lib/Target/NVIDIA/IR/Target.cpp:62-86).  Requires unit innermost strides,
- * D == DV == 128 (64 also accepted), other strides multiples of 8 elements.
+ * D == DV == 128, other strides positive multiples of 8 elements, 16-byte
+ * aligned bases and scale > 0.  An empty key sequence yields zeros.
  */
 int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
                          int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,

@@ -114,7 +114,7 @@ def test_gemm_is_linear_in_a():
 # ---------------------------------------------------------------- attention
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("b,h,s,d", [(1, 2, 256, 128), (2, 3, 300, 128), (1, 1, 128, 128), (1, 2, 1000, 128),
-                                     (1, 1, 17, 128), (1, 2, 384, 64)])
+                                     (1, 1, 17, 128), (1, 2, 4096, 128)])
 def test_flash_attention_causal(dtype, b, h, s, d):
     q, k, v, scale = workloads.attention_inputs(b, h, s, d, seed=s, dtype=dtype)
     out = ops.flash_attention(*cuda(q, k, v), scale)
@@ -135,6 +135,12 @@ def test_flash_attention_gqa_noncausal_and_rectangular():
     few = ops.flash_attention(*cuda(q[:, :, :50], k, v), scale, head_group=4)
     assert relative_error(few, oracle.attention(q[:, :, :50].contiguous(), k, v, scale, head_group=4)) <= 1e-2
     ops.workspace_status(DEV)
+
+
+def test_flash_attention_refuses_other_head_dimensions():
+    q, k, v, scale = workloads.attention_inputs(1, 2, 64, 64, seed=3)
+    with pytest.raises(NotImplementedError, match="head dimensions"):
+        ops.flash_attention(*cuda(q, k, v), scale)
 
 
 def test_flash_attention_strided_heads():
