@@ -209,9 +209,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int i = 0; i < kBlockN; ++i)
           if (i >= limit) s[i] = -INFINITY;
       }
-      float tile_max = s[0];
+      // eight independent running maxima keep the dependent chain 16 deep instead of 128
+      float partial_max[8];
 #pragma unroll
-      for (int i = 1; i < kBlockN; ++i) tile_max = fmaxf(tile_max, s[i]);
+      for (int u = 0; u < 8; ++u) partial_max[u] = s[u];
+#pragma unroll
+      for (int i = 8; i < kBlockN; i += 8)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) partial_max[u] = fmaxf(partial_max[u], s[i + u]);
+      float tile_max = fmaxf(fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])),
+                             fmaxf(fmaxf(partial_max[4], partial_max[5]), fmaxf(partial_max[6], partial_max[7])));
       tile_max *= shape.scale_log2;
       // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
       const bool grow = tile_max > reference + kRescaleThreshold;
@@ -232,6 +239,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
       const float offset = -reference;
+      float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int chunk = 0; chunk < kBlockN / 64; ++chunk) {
         uint32_t packed[32];
@@ -239,11 +247,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int i = 0; i < 32; ++i) {
           const float p0 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i], shape.scale_log2, offset));
           const float p1 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i + 1], shape.scale_log2, offset));
-          sum += p0 + p1;
+          partial_sum[(2 * i) & 3] += p0;
+          partial_sum[(2 * i + 1) & 3] += p1;
           packed[i] = pack_pair<T>(p0, p1);
         }
         tc::tmem_store_32x32(tmem_s + lane_base + chunk * 32, packed);
       }
+      sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
       tc::tmem_store_wait();
       tc::tc_fence_before_sync();
       __syncwarp();
