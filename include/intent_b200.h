@@ -195,6 +195,15 @@ int b200_csr_validate(const void *row_offsets, int64_t rows, const void *column_
                       int64_t nnz, int64_t columns, int64_t *where, void *stream);
 
 /*
+ * b200_csr_spmm waits for its staged gathers with a bound.  If such a wait
+ * ever gave up, the affected row was left unwritten and a device-side flag was
+ * raised; this call synchronises `stream`, returns B200_ERR_DEVICE_TIMEOUT
+ * (clearing the flag) and stores the row in *row (may be null), else B200_OK.
+ * No counterpart in the reference.
+ */
+int b200_csr_spmm_status(int64_t *row, void *stream);
+
+/*
  * Reads word 0 of a workspace after synchronising `stream`: B200_OK, or
  * B200_ERR_DEVICE_TIMEOUT when a bounded wait inside a kernel gave up.
  * `detail` (may be null) receives word 1, which names the wait that ran out.

@@ -1,13 +1,19 @@
 // CSR SpMM  Y = A . X  (i32 indices, f32 values).
 //
-// One warp owns one output row.  The 32 lanes cover 128 features with one
-// float4 each, so a gathered row of X is one coalesced 512-byte read; column
-// indices and values are fetched 32 at a time (coalesced) and broadcast with
-// shuffles.  Terms are added strictly in storage order with a separately
-// rounded multiply and add, so the result equals a sequential left-to-right
-// evaluation bit for bit.  Algorithmic (compulsory) traffic per launch:
+// One warp owns one output row at a time and walks over rows in a persistent
+// loop.  The 32 lanes cover 128 features with one float4 each, so a gathered
+// row of X is one coalesced 512-byte read; column indices and values are
+// fetched 32 at a time (coalesced) and broadcast with shuffles.  The kernel is
+// bound by memory latency, not bandwidth, so it keeps as many gathers in flight
+// as the register file allows: all (up to) 32 gathers of a batch are issued
+// before the first is consumed, and the next row's offsets, indices and values
+// are requested while they are in flight.  Terms are added strictly in storage
+// order with a separately rounded multiply and add, so the result equals a
+// sequential left-to-right evaluation bit for bit.  Algorithmic (compulsory) traffic per launch:
 // (rows+1)*4 + nnz*8 + columns*F*4 + rows*F*4 bytes; the gathers of X are
 // served by L2 where they hit.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -84,6 +90,171 @@ csr_spmm_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restri
   }
 }
 
+// ---------------------------------------------------------------------------
+// Vector path.  The gathers are latency-bound, so they are handed to the copy
+// engine instead of being held in registers: lane j of the warp that owns a row
+// issues ONE bulk asynchronous copy (cp.async.bulk, global -> shared, 512 bytes
+// for 128 features) for the j-th non-zero's row of X; the up-to-32 copies of a
+// batch complete on one mbarrier.  Every warp owns kStages staging buffers of
+// 32 x 512 bytes and requests batch i+1 while it folds batch i, so an SM keeps
+// kWarps x kStages x 16 KB (224 KB) of gathers in flight with no register cost.
+// The fold reads the staged rows back in storage order (lane l takes features
+// 4l..4l+3, conflict-free) and keeps the separately rounded multiply and add.
+// ---------------------------------------------------------------------------
+constexpr int kBulkWarps = 7;
+constexpr int kBulkStages = 2;
+constexpr int kBulkRowBytes = 512;                       // 128 features
+constexpr int kBulkStageBytes = 32 * kBulkRowBytes;      // one batch of 32 non-zeros
+constexpr size_t kBulkSmemBytes = (size_t)kBulkWarps * kBulkStages * kBulkStageBytes + kBulkWarps * kBulkStages * 8 + 16;
+constexpr long long kBulkWaitCycles = 4000000000ll;      // ~2 s: a copy that has not landed by then never will
+
+__device__ int spmm_status[2];  // {sticky flag, row that gave up}
+
+__device__ __forceinline__ uint32_t shared_address(const void *pointer) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+struct Batch {
+  int column;     // this lane's column index (lane j <-> j-th non-zero of the batch)
+  float value;
+  int count;      // non-zeros in the batch (0..32)
+};
+
+__global__ void __launch_bounds__(kBulkWarps * 32, 1)
+csr_spmm_bulk_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
+                     const float *__restrict__ values, const float *__restrict__ dense,
+                     float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
+                     int64_t output_pitch) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int feature0 = blockIdx.y * 128;
+  const int width = min(128, features - feature0);         // features of this chunk
+  const uint32_t row_bytes = (uint32_t)width * 4;
+  const bool active = lane * 4 < width;
+  unsigned char *stage_base = bulk_smem + (size_t)warp * kBulkStages * kBulkStageBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)kBulkWarps * kBulkStages * kBulkStageBytes) +
+                   warp * kBulkStages;
+  if (lane == 0) {
+    for (int s = 0; s < kBulkStages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(bars + s)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int64_t warps = (int64_t)gridDim.x * kBulkWarps;
+  int64_t row = (int64_t)blockIdx.x * kBulkWarps + warp;
+  if (row >= rows) return;
+  const float *source = dense + feature0;
+
+  // Requests the gathers of one batch into `stage`; lane j copies non-zero j's row of X.
+  auto request = [&](int stage, int base, int stop) -> Batch {
+    Batch batch;
+    batch.count = max(0, min(32, stop - base));
+    batch.column = 0;
+    batch.value = 0.0f;
+    if (lane < batch.count) {
+      batch.column = __ldcs(column_indices + base + lane);
+      batch.value = __ldcs(values + base + lane);
+    }
+    const uint32_t bar = shared_address(bars + stage);
+    if (lane == 0 && batch.count > 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(batch.count * row_bytes)
+                   : "memory");
+    __syncwarp();
+    if (lane < batch.count) {
+      const float *from = source + (int64_t)batch.column * dense_pitch;
+      const uint32_t to = shared_address(stage_base + stage * kBulkStageBytes + lane * kBulkRowBytes);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(to), "l"(from), "r"(row_bytes), "r"(bar)
+                   : "memory");
+    }
+    return batch;
+  };
+
+  int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
+  int stage = 0;
+  uint32_t parity[kBulkStages];
+#pragma unroll
+  for (int s = 0; s < kBulkStages; ++s) parity[s] = 0;
+  int base = start;
+  Batch current = request(stage, base, stop);
+  bool alive = true;
+  while (alive) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    int64_t next_row = row + warps;
+    while (true) {
+      // what comes after the current batch: the rest of this row, or the first batch of the next row
+      const bool more_in_row = base + 32 < stop;
+      int following_start = 0, following_stop = 0;
+      const bool has_following = more_in_row || next_row < rows;
+      if (more_in_row) {
+        following_start = base + 32;
+        following_stop = stop;
+      } else if (next_row < rows) {
+        following_start = __ldg(row_offsets + next_row);
+        following_stop = __ldg(row_offsets + next_row + 1);
+      }
+      const int other = (stage + 1) % kBulkStages;
+      Batch following;
+      following.count = 0; following.column = 0; following.value = 0.0f;
+      if (has_following) following = request(other, following_start, following_stop);
+
+      if (current.count > 0) {
+        const uint32_t bar = shared_address(bars + stage);
+        uint32_t done = 0;
+        const long long begin = clock64();
+        while (true) {
+          asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                       : "=r"(done) : "r"(bar), "r"(parity[stage]) : "memory");
+          if (done) break;
+          if (clock64() - begin > kBulkWaitCycles) break;
+        }
+        if (!done) {  // give up: flag the failure, leave the row unwritten and stop this warp
+          if (lane == 0 && atomicCAS(&spmm_status[0], 0, 1) == 0) spmm_status[1] = (int)row;
+          if (following.count > 0) {  // let the batch already requested land before the buffers go away
+            const uint32_t other_bar = shared_address(bars + other);
+            const long long drain = clock64();
+            uint32_t landed = 0;
+            while (!landed && clock64() - drain < kBulkWaitCycles / 8)
+              asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                           : "=r"(landed) : "r"(other_bar), "r"(parity[other]) : "memory");
+          }
+          alive = false;
+          break;
+        }
+        parity[stage] ^= 1;
+        const unsigned char *staged = stage_base + stage * kBulkStageBytes + lane * 16;
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+          const float weight = __shfl_sync(0xffffffffu, current.value, j);
+          if (active && j < current.count) {
+            const float4 x = *reinterpret_cast<const float4 *>(staged + j * kBulkRowBytes);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x.x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x.w));
+          }
+        }
+        __syncwarp();  // every lane has read the stage before it is requested again
+      }
+      stage = other;
+      current = following;
+      if (more_in_row) {
+        base += 32;
+        continue;
+      }
+      if (active) __stcs(reinterpret_cast<float4 *>(output + row * output_pitch + feature0 + lane * 4), acc);
+      if (next_row >= rows) alive = false;
+      row = next_row;
+      start = following_start;
+      stop = following_stop;
+      base = start;
+      break;
+    }
+  }
+  // No copy is left in flight here on the normal path: every requested batch was waited for.
+}
+
 // result[0] = first bad position + 1 (0 = valid); atomicMin over positions.
 __global__ void csr_validate_kernel(const int32_t *__restrict__ row_offsets, int64_t rows,
                                     const int32_t *__restrict__ column_indices, int64_t nnz,
@@ -129,11 +300,21 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
   const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
   if (ctas > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmm: too many rows");
   const bool vector = x_d1 % 4 == 0 && x_s0 % 4 == 0 && y_s0 % 4 == 0 && aligned16(dense) && aligned16(output);
-  if (vector)
-    csr_spmm_kernel<true><<<(unsigned)ctas, kWarpsPerCta * 32, 0, s>>>(
+  if (vector) {
+    static std::once_flag configured;
+    static cudaError_t attribute_error = cudaSuccess;
+    std::call_once(configured, [] {
+      attribute_error = cudaFuncSetAttribute(csr_spmm_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kBulkSmemBytes);
+    });
+    B200_CUDA_TRY(attribute_error);
+    const int64_t wanted = (rows + kBulkWarps - 1) / kBulkWarps;
+    const int64_t resident = sm_count();
+    const dim3 grid((unsigned)(wanted < resident ? wanted : resident), (unsigned)((x_d1 + 127) / 128));
+    csr_spmm_bulk_kernel<<<grid, kBulkWarps * 32, kBulkSmemBytes, s>>>(
         (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
         (const float *)dense, (float *)output, rows, (int)x_d1, x_s0, y_s0);
-  else
+  } else
     csr_spmm_kernel<false><<<(unsigned)ctas, kWarpsPerCta * 32, 0, s>>>(
         (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
         (const float *)dense, (float *)output, rows, (int)x_d1, x_s0, y_s0);
@@ -165,6 +346,20 @@ extern "C" int b200_csr_validate(const void *row_offsets, int64_t rows, const vo
     if (where) *where = position;
     return fail(B200_ERR_INVALID_ARGUMENT, "csr_validate: %s[%lld] is out of range",
                 host <= (unsigned long long)rows ? "row_offsets" : "column_indices", (long long)position);
+  }
+  return B200_OK;
+}
+
+extern "C" int b200_csr_spmm_status(int64_t *row, void *stream) {
+  int words[2] = {0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B200_CUDA_TRY(cudaMemcpyFromSymbolAsync(words, spmm_status, sizeof words, 0, cudaMemcpyDeviceToHost, s));
+  B200_CUDA_TRY(cudaStreamSynchronize(s));
+  if (row) *row = words[1];
+  if (words[0] != 0) {
+    const int zero[2] = {0, 0};
+    cudaMemcpyToSymbolAsync(spmm_status, zero, sizeof zero, 0, cudaMemcpyHostToDevice, s);
+    return fail(B200_ERR_DEVICE_TIMEOUT, "csr_spmm: a staged gather did not arrive (row %d left unwritten)", words[1]);
   }
   return B200_OK;
 }

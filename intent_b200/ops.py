@@ -112,6 +112,15 @@ def csr_spmm(row_offsets, column_indices, values, dense, out=None):
     return out
 
 
+def csr_spmm_status(device) -> None:
+    """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
+    device = torch.device(device)
+    row = ctypes.c_int64(-1)
+    with torch.cuda.device(device):
+        status = _native.entry("b200_csr_spmm_status")(ctypes.byref(row), torch.cuda.current_stream(device).cuda_stream)
+    _native.check("b200_csr_spmm_status", status)
+
+
 def csr_validate(row_offsets, column_indices, columns: int) -> None:
     device = _require_cuda(row_offsets, column_indices)
     where = ctypes.c_int64(-1)
