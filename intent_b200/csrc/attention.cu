@@ -1,25 +1,31 @@
 // Flash-attention forward on the tcgen05 tensor cores (bf16 / f16, head dim 128).
 //
-// One CTA owns one tile of 128 query rows of one (batch, head) and streams the
-// key/value sequence through it in tiles of 128 keys.  Two CTAs are resident per
-// SM (256 TMEM columns and ~97 KB of shared memory each), so while one CTA's
-// softmax warps work on a score tile the other CTA's MMAs keep the tensor pipe
-// busy.
+// One CTA per SM owns TWO tiles of 128 query rows (A and B, 256 consecutive rows
+// of one (batch, head)) and streams the key/value sequence through them in tiles
+// of 128 keys.  The single MMA-issuing thread interleaves the two tiles,
 //
-//   warp 0      TMA producer: Q once, then K_j / V_j into two 32 KB slots
-//               (128 rows x 128 B, two 64-column halves, 128-byte swizzle)
+//     S_A(j)   P.V_B(j-1)   S_B(j)   P.V_A(j)   S_A(j+1)   ...
+//
+// so that while the softmax warps of one tile work on their scores the tensor
+// pipe runs the other tile's two MMAs: each softmax has two MMA slots of cover.
+//
+//   warp 0      TMA producer: Q_A, Q_B once, then K_j, V_j, K_j+1, ... through a
+//               ring of five 32 KB slots (128 rows x 128 B in two 64-column
+//               halves, 128-byte swizzle)
 //   warp 1      MMA issuer:  S = Q . K_j^T   (A, B from shared memory, K-major)
 //                            O += P . V_j    (A = P from TMEM, B = V MN-major)
-//   warps 2..5  softmax: thread r owns query row r.  tcgen05.ld the 128 scores,
-//               row maximum, p = ex2.approx.ftz(s*scale*log2e - m), f32 row sum,
-//               P rounded to the operand type and written back over the score
-//               columns (tcgen05.st); the running maximum is only replaced, and O
-//               and the sum rescaled, when it grows by more than 2^8, which keeps
-//               the accumulator exact in the usual online-softmax sense while
-//               rescales stay rare.  Last: O * div.approx.ftz(1, sum) -> global.
+//   warps 2..5  softmax of tile A, warps 6..9 softmax of tile B: thread r owns
+//               query row r of its tile.  tcgen05.ld the 128 scores, row maximum,
+//               p = ex2.approx.ftz(s*scale*log2e - m), f32 row sum, P rounded to
+//               the operand type and written back over the score columns
+//               (tcgen05.st).  The running maximum is only replaced, and O and the
+//               sum rescaled, when it grows by more than 2^8: the accumulator stays
+//               exact in the usual online-softmax sense while rescales stay rare.
+//               Last: O * div.approx.ftz(1, sum) -> global.
 //
-// TMEM: columns [0,128) scores S (P aliases [0,64)), [128,256) accumulator O.
-// Causal tiles that lie entirely above the diagonal are never visited; the
+// TMEM (512 columns): S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512);
+// P aliases the first 64 columns of its S.  Causal tiles that lie entirely above
+// the diagonal are never visited (tile A stops one key tile before tile B); the
 // diagonal tile and the ragged last key tile are masked element-wise.
 // Work per launch: 4*B*H*D*S*(S+1)/2 flop (causal), 4*B*H*S*D*2 compulsory bytes.
 #include <mutex>
@@ -30,22 +36,25 @@
 namespace b200 {
 namespace {
 
-constexpr int kBlockM = 128;
+constexpr int kBlockM = 128;                     // query rows per tile (two tiles per CTA)
 constexpr int kBlockN = 128;
 constexpr int kHeadDim = 128;
-constexpr int kThreads = 192;
-constexpr int kTmemColumns = 256;
+constexpr int kThreads = 320;
+constexpr int kTmemColumns = 512;
+constexpr int kRingSlots = 5;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one Q / K / V tile
 constexpr uint32_t kHalfBytes = kTileBytes / 2;  // 64-column half
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
 struct __align__(8) Barriers {
-  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_ready, o_full;
+  uint64_t q_full;
+  uint64_t slot_full[kRingSlots], slot_empty[kRingSlots];
+  uint64_t s_full[2], p_ready[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr size_t kSmemBytes = 1024 + 3 * kTileBytes + sizeof(Barriers);
+constexpr size_t kSmemBytes = 1024 + (2 + kRingSlots) * kTileBytes + sizeof(Barriers);
 
 struct Shape {
   int batch, heads_q, seq_q, seq_k, head_group, causal;
@@ -74,35 +83,52 @@ template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float l
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// Ring bookkeeping shared by producer and consumer: tile i of the K0,V0,K1,V1,.. stream
+// lives in slot i % kRingSlots and completes that slot's barriers for the (i / kRingSlots)-th time.
+struct RingPosition {
+  int slot;
+  uint32_t phase;
+  __device__ explicit RingPosition(int index) : slot(index % kRingSlots), phase((index / kRingSlots) & 1) {}
+};
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const Shape shape, int *status) {
   extern __shared__ unsigned char raw_smem[];
   unsigned char *tiles = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
-  unsigned char *q_tile = tiles, *k_tile = tiles + kTileBytes, *v_tile = tiles + 2 * kTileBytes;
-  Barriers *bars = reinterpret_cast<Barriers *>(tiles + 3 * kTileBytes);
+  unsigned char *q_tiles = tiles;                       // Q_A, Q_B
+  unsigned char *ring = tiles + 2 * kTileBytes;         // kRingSlots tiles
+  Barriers *bars = reinterpret_cast<Barriers *>(tiles + (2 + kRingSlots) * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heaviest query tiles (most key tiles under the causal mask) are scheduled first
-  const int q_tiles = (shape.seq_q + kBlockM - 1) / kBlockM;
-  const int q_tile_index = q_tiles - 1 - (int)blockIdx.x;
+  const int pairs = (shape.seq_q + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int pair = pairs - 1 - (int)blockIdx.x;
   const int head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / shape.head_group;
-  const int q0 = q_tile_index * kBlockM;
-  int key_tiles = (shape.seq_k + kBlockN - 1) / kBlockN;
-  if (shape.causal) key_tiles = min(key_tiles, (q0 + kBlockM - 1) / kBlockN + 1);
+  const int q0 = pair * 2 * kBlockM;                    // first row of tile A; tile B starts at q0 + 128
+  const int all_key_tiles = (shape.seq_k + kBlockN - 1) / kBlockN;
+  int tiles_of[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    tiles_of[x] = all_key_tiles;
+    if (shape.causal) tiles_of[x] = min(all_key_tiles, (q0 + x * kBlockM + kBlockM - 1) / kBlockN + 1);
+  }
+  const int key_tiles = max(tiles_of[0], tiles_of[1]);  // = tiles_of[1]
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&bars->q_full, 1);
-    tc::mbar_init(&bars->k_full, 1);
-    tc::mbar_init(&bars->k_empty, 1);
-    tc::mbar_init(&bars->v_full, 1);
-    tc::mbar_init(&bars->v_empty, 1);
-    tc::mbar_init(&bars->s_full, 1);
-    tc::mbar_init(&bars->p_ready, 4);
-    tc::mbar_init(&bars->o_full, 1);
+    for (int s = 0; s < kRingSlots; ++s) {
+      tc::mbar_init(&bars->slot_full[s], 1);
+      tc::mbar_init(&bars->slot_empty[s], 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      tc::mbar_init(&bars->s_full[x], 1);
+      tc::mbar_init(&bars->p_ready[x], 4);
+      tc::mbar_init(&bars->o_full[x], 1);
+    }
     bars->abort_flag = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_descriptor(&map_q);
@@ -114,36 +140,41 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kBlockN;
   volatile int *abort_flag = &bars->abort_flag;
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (tc::elect_one()) {
-      tc::mbar_expect_tx(&bars->q_full, kTileBytes);
-      tc::tma_load_4d(q_tile, &map_q, &bars->q_full, 0, q0, head, batch);
-      tc::tma_load_4d(q_tile + kHalfBytes, &map_q, &bars->q_full, 64, q0, head, batch);
-      int loaded_k = 0, loaded_v = 0;
+      tc::mbar_expect_tx(&bars->q_full, 2 * kTileBytes);
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        tc::tma_load_4d(q_tiles + x * kTileBytes, &map_q, &bars->q_full, 0, q0 + x * kBlockM, head, batch);
+        tc::tma_load_4d(q_tiles + x * kTileBytes + kHalfBytes, &map_q, &bars->q_full, 64, q0 + x * kBlockM, head, batch);
+      }
+      int issued = 0;
       bool alive = true;
-      for (int j = 0; alive && j < key_tiles; ++j) {
-        const uint32_t phase = j & 1;
-        if (!tc::mbar_wait(&bars->k_empty, phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) { alive = false; break; }
-        tc::mbar_expect_tx(&bars->k_full, kTileBytes);
-        tc::tma_load_4d(k_tile, &map_k, &bars->k_full, 0, j * kBlockN, kv_head, batch);
-        tc::tma_load_4d(k_tile + kHalfBytes, &map_k, &bars->k_full, 64, j * kBlockN, kv_head, batch);
-        ++loaded_k;
-        if (!tc::mbar_wait(&bars->v_empty, phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) { alive = false; break; }
-        tc::mbar_expect_tx(&bars->v_full, kTileBytes);
-        tc::tma_load_4d(v_tile, &map_v, &bars->v_full, 0, j * kBlockN, kv_head, batch);
-        tc::tma_load_4d(v_tile + kHalfBytes, &map_v, &bars->v_full, 64, j * kBlockN, kv_head, batch);
-        ++loaded_v;
+      for (int index = 0; index < 2 * key_tiles; ++index) {  // K0, V0, K1, V1, ...
+        const RingPosition at(index);
+        if (!tc::mbar_wait(&bars->slot_empty[at.slot], at.phase ^ 1, abort_flag, status, tc::kSiteProducerEmpty)) {
+          alive = false;
+          break;
+        }
+        unsigned char *slot = ring + at.slot * kTileBytes;
+        const CUtensorMap *map = (index & 1) ? &map_v : &map_k;
+        const int key0 = (index >> 1) * kBlockN;
+        tc::mbar_expect_tx(&bars->slot_full[at.slot], kTileBytes);
+        tc::tma_load_4d(slot, map, &bars->slot_full[at.slot], 0, key0, kv_head, batch);
+        tc::tma_load_4d(slot + kHalfBytes, map, &bars->slot_full[at.slot], 64, key0, kv_head, batch);
+        ++issued;
       }
       if (!alive) {
         // let copies in flight land before the shared memory goes away
         const long long start = clock64();
         while (!tc::mbar_try_wait(&bars->q_full, 0) && clock64() - start < tc::kWaitCycles / 8) {}
-        if (loaded_k) while (!tc::mbar_try_wait(&bars->k_full, (loaded_k - 1) & 1) && clock64() - start < tc::kWaitCycles / 8) {}
-        if (loaded_v) while (!tc::mbar_try_wait(&bars->v_full, (loaded_v - 1) & 1) && clock64() - start < tc::kWaitCycles / 8) {}
+        for (int back = 1; back <= min(issued, kRingSlots); ++back) {
+          const RingPosition at(issued - back);
+          while (!tc::mbar_try_wait(&bars->slot_full[at.slot], at.phase) && clock64() - start < tc::kWaitCycles / 8) {}
+        }
       }
     }
   } else if (warp == 1) {
@@ -152,45 +183,74 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       constexpr int format = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = tc::instr_desc_f16(format, kBlockM, kBlockN, false);
       constexpr uint32_t idesc_o = tc::instr_desc_f16(format, kBlockM, kHeadDim, true);
+      const uint32_t ring_address = tc::smem_u32(ring);
       bool alive = tc::mbar_wait(&bars->q_full, 0, abort_flag, status, tc::kSiteMmaFull);
-      const uint32_t q_address = tc::smem_u32(q_tile), k_address = tc::smem_u32(k_tile), v_address = tc::smem_u32(v_tile);
-      for (int j = 0; alive && j < key_tiles; ++j) {
-        const uint32_t phase = j & 1;
-        if (!tc::mbar_wait(&bars->k_full, phase, abort_flag, status, tc::kSiteMmaFull)) break;
-        tc::tc_fence_after_sync();
+
+      // S_x(j) = Q_x . K_j^T into the score columns of tile x
+      auto issue_scores = [&](int x, int j) {
+        const uint32_t q_address = tc::smem_u32(q_tiles + x * kTileBytes);
+        const uint32_t k_address = ring_address + RingPosition(2 * j).slot * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk) {
           const uint32_t offset = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-          tc::mma_f16_ss(tmem_s, tc::smem_desc_k_major_sw128(q_address + offset),
+          tc::mma_f16_ss(tmem_base + x * kBlockN, tc::smem_desc_k_major_sw128(q_address + offset),
                          tc::smem_desc_k_major_sw128(k_address + offset), idesc_s, kk != 0);
         }
-        tc::mma_commit(&bars->k_empty);
-        tc::mma_commit(&bars->s_full);
-        if (!tc::mbar_wait(&bars->v_full, phase, abort_flag, status, tc::kSiteMmaFull)) break;
-        if (!tc::mbar_wait(&bars->p_ready, phase, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
+        tc::mma_commit(&bars->s_full[x]);
+      };
+      // O_x += P_x(j) . V_j; P is read from the first 64 (packed) score columns of tile x
+      auto issue_values = [&](int x, int j) -> bool {
+        if (!tc::mbar_wait(&bars->p_ready[x], j & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) return false;
         tc::tc_fence_after_sync();
+        const uint32_t v_address = ring_address + RingPosition(2 * j + 1).slot * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // A: 16 keys = 8 packed TMEM columns; B: 16 key rows = 2048 bytes further down the V tile
-          tc::mma_f16_ts(tmem_o, tmem_s + kk * 8, tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes),
-                         idesc_o, (j | kk) != 0);
+          tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kHeadDim, tmem_base + x * kBlockN + kk * 8,
+                         tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes), idesc_o, (j | kk) != 0);
         }
-        tc::mma_commit(&bars->v_empty);
-        if (j == key_tiles - 1) tc::mma_commit(&bars->o_full);
+        if (j == tiles_of[x] - 1) tc::mma_commit(&bars->o_full[x]);
+        return true;
+      };
+      auto wait_slot = [&](int index) {
+        const RingPosition at(index);
+        const bool ok = tc::mbar_wait(&bars->slot_full[at.slot], at.phase, abort_flag, status, tc::kSiteMmaFull);
+        tc::tc_fence_after_sync();
+        return ok;
+      };
+      auto release_slot = [&](int index) { tc::mma_commit(&bars->slot_empty[RingPosition(index).slot]); };
+
+      for (int j = 0; alive && j < key_tiles; ++j) {
+        if (!wait_slot(2 * j)) break;                                   // K_j
+        if (j < tiles_of[0]) issue_scores(0, j);
+        if (j >= 1) {                                                   // P.V_B(j-1): covers softmax A(j)
+          if (!wait_slot(2 * j - 1) || !issue_values(1, j - 1)) { alive = false; break; }
+          release_slot(2 * j - 1);                                      // V_(j-1): both tiles are done with it
+        }
+        issue_scores(1, j);                                             // tile B sees every key tile
+        release_slot(2 * j);                                            // K_j
+        if (j < tiles_of[0]) {                                          // P.V_A(j): covers softmax B(j)
+          if (!wait_slot(2 * j + 1) || !issue_values(0, j)) { alive = false; break; }
+        }
       }
+      if (alive && wait_slot(2 * key_tiles - 1) && issue_values(1, key_tiles - 1)) release_slot(2 * key_tiles - 1);
     }
   } else {
     // -------------------------------------------------------------- softmax
-    const int quadrant = warp & 3;
+    const int x = (warp - 2) >> 2;                // 0: tile A (warps 2..5), 1: tile B (warps 6..9)
+    const int quadrant = warp & 3;                // TMEM lanes [32*quadrant, +32) are this warp's
     const int row_in_tile = quadrant * 32 + lane;
-    const int q_row = q0 + row_in_tile;
+    const int tile_q0 = q0 + x * kBlockM;
+    const int q_row = tile_q0 + row_in_tile;
+    const int my_tiles = tiles_of[x];
     const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+    const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kHeadDim;
     float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
     float sum = 0.0f;
     bool alive = true;
-    for (int j = 0; alive && j < key_tiles; ++j) {
+    for (int j = 0; alive && j < my_tiles; ++j) {
       const uint32_t phase = j & 1;
-      if (!tc::mbar_wait(&bars->s_full, phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
+      if (!tc::mbar_wait(&bars->s_full[x], phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
       tc::tc_fence_after_sync();
       float s[kBlockN];
 #pragma unroll
@@ -202,7 +262,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       tc::tmem_load_wait();
       const int k0 = j * kBlockN;
-      const bool masked_tile = (k0 + kBlockN > shape.seq_k) || (shape.causal && k0 + kBlockN - 1 > q0);
+      const bool masked_tile = (k0 + kBlockN > shape.seq_k) || (shape.causal && k0 + kBlockN - 1 > tile_q0);
       if (masked_tile) {
         const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
 #pragma unroll
@@ -226,7 +286,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float factor = grow ? ex2_approx_ftz(reference - tile_max) : 1.0f;  // 0 on the first tile
         if (grow) { reference = tile_max; sum *= factor; }
         if (j > 0) {
-          // S(j) has completed, hence P.V(j-1) too: O is quiescent until p_ready is signalled
+          // S(j) has completed, hence this tile's P.V(j-1) too: O is quiescent until p_ready is signalled
 #pragma unroll 1
           for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
             uint32_t raw[32];
@@ -257,9 +317,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc::tmem_store_wait();
       tc::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&bars->p_ready);
+      if (lane == 0) tc::mbar_arrive(&bars->p_ready[x]);
     }
-    if (alive && tc::mbar_wait(&bars->o_full, 0, abort_flag, status, tc::kSiteEpilogueTmemFull)) {
+    if (alive && tc::mbar_wait(&bars->o_full[x], 0, abort_flag, status, tc::kSiteEpilogueTmemFull)) {
       tc::tc_fence_after_sync();
       const float inverse = div_approx_ftz(1.0f, sum);
       T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s;
@@ -354,7 +414,7 @@ int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd,
   shape.head_group = head_group; shape.causal = causal;
   shape.o_stride_b = os[0]; shape.o_stride_h = os[1]; shape.o_stride_s = os[2];
   shape.scale_log2 = scale * (float)1.4426950408889634;  // scale * LOG2E, rounded to f32 like the kernel definition
-  const dim3 grid((unsigned)((seq_q + kBlockM - 1) / kBlockM), (unsigned)heads_q, (unsigned)batch);
+  const dim3 grid((unsigned)((seq_q + 2 * kBlockM - 1) / (2 * kBlockM)), (unsigned)heads_q, (unsigned)batch);
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, o, shape, status);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
