@@ -14,18 +14,23 @@ namespace {
 
 constexpr int kCtaWarps = 8;
 
-template <int WARPS> struct GroupShape {
-  static constexpr int kCtaThreads = (WARPS > kCtaWarps ? WARPS : kCtaWarps) * 32;
+// CTA_WARPS: warps per CTA when a row needs fewer.  Softmax uses small CTAs so
+// that a few thousand rows still spread evenly over 148 SMs.
+template <int WARPS, int CTA_WARPS = kCtaWarps> struct GroupShape {
+  static constexpr int kCtaThreads = (WARPS > CTA_WARPS ? WARPS : CTA_WARPS) * 32;
   static constexpr int kGroups = kCtaThreads / (WARPS * 32);
 };
 
 // ------------------------------------------------------------------ softmax
+constexpr int kSoftmaxCtaWarps = 4;
+template <int WARPS> using SoftmaxShape = GroupShape<WARPS, kSoftmaxCtaWarps>;
+
 template <typename T, int WARPS, int ITERS>
-__global__ void __launch_bounds__(GroupShape<WARPS>::kCtaThreads)
+__global__ void __launch_bounds__(SoftmaxShape<WARPS>::kCtaThreads)
 softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int columns,
                     int64_t x_pitch, int64_t y_pitch) {
   constexpr int kVec = Element<T>::kVec;
-  constexpr int kGroups = GroupShape<WARPS>::kGroups;
+  constexpr int kGroups = SoftmaxShape<WARPS>::kGroups;
   constexpr int kRowThreads = WARPS * 32;
   __shared__ float scratch[kGroups][2][WARPS];
   const int group = threadIdx.x / kRowThreads;
@@ -278,7 +283,7 @@ int grid_for(int64_t rows, int groups_per_cta, int ctas_per_sm) {
 template <typename T, int WARPS, int ITERS>
 int launch_softmax_rows(const T *x, T *y, int64_t rows, int64_t columns, int64_t xp, int64_t yp,
                         cudaStream_t stream) {
-  using Shape = GroupShape<WARPS>;
+  using Shape = SoftmaxShape<WARPS>;
   const int grid = grid_for(rows, Shape::kGroups, 2048 / Shape::kCtaThreads);
   softmax_rows_kernel<T, WARPS, ITERS><<<grid, Shape::kCtaThreads, 0, stream>>>(
       x, y, rows, (int)columns, xp, yp);

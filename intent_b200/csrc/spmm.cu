@@ -1,17 +1,22 @@
 // CSR SpMM  Y = A . X  (i32 indices, f32 values).
 //
-// One warp owns one output row at a time and walks over rows in a persistent
-// loop.  The 32 lanes cover 128 features with one float4 each, so a gathered
-// row of X is one coalesced 512-byte read; column indices and values are
-// fetched 32 at a time (coalesced) and broadcast with shuffles.  The kernel is
-// bound by memory latency, not bandwidth, so it keeps as many gathers in flight
-// as the register file allows: all (up to) 32 gathers of a batch are issued
-// before the first is consumed, and the next row's offsets, indices and values
-// are requested while they are in flight.  Terms are added strictly in storage
-// order with a separately rounded multiply and add, so the result equals a
-// sequential left-to-right evaluation bit for bit.  Algorithmic (compulsory) traffic per launch:
-// (rows+1)*4 + nnz*8 + columns*F*4 + rows*F*4 bytes; the gathers of X are
-// served by L2 where they hit.
+// One warp owns one output row; its 32 lanes cover 128 features with one float4
+// each, so a gathered row of X is one coalesced 512-byte read.  Column indices
+// and values are fetched 32 at a time (coalesced) and broadcast with shuffles.
+// Terms are added strictly in storage order with a separately rounded multiply
+// and add, so the result equals a sequential left-to-right evaluation bit for
+// bit.  Three kernels share that scheme:
+//   csr_spmm_bulk_kernel   X fits L2 (one launch): gathers are staged through
+//                          shared memory by the copy engine (cp.async.bulk),
+//                          224 KB in flight per SM, software-pipelined rows
+//   csr_spmm_block_kernel  X larger than L2: the call is cut into column blocks,
+//                          one launch each, accumulating into Y; gathers in
+//                          registers, many warps
+//   csr_spmm_kernel        any feature count / alignment (scalar fallback)
+// Algorithmic (compulsory) traffic per call: (rows+1)*4 + nnz*8 + columns*F*4 +
+// rows*F*4 bytes; the gathers touch nnz*F*4 bytes and are served by L2 where they hit.
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -114,18 +119,45 @@ __device__ __forceinline__ uint32_t shared_address(const void *pointer) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }
 
-struct Batch {
-  int column;     // this lane's column index (lane j <-> j-th non-zero of the batch)
-  float value;
-  int count;      // non-zeros in the batch (0..32)
-};
+
+// Column-blocked execution.  X (columns x F x 4 bytes) is larger than L2 for the
+// benchmark shape, and random 512-byte gathers that miss L2 run at a fraction of
+// HBM's streaming rate.  So one call is split into launches that each cover a
+// block of columns small enough to (mostly) stay in L2: launch p adds the terms whose
+// column lies in block p to Y (read-modify-write, streamed).  With ascending
+// columns inside every row the blocks are visited in storage order, so the sum
+// of a row is still accumulated strictly left to right.  `spmm_sorted` is set by
+// a check pass at the start of the call; if some row is not ascending, launch 0
+// covers every column and the other launches return at once.
+__device__ int spmm_sorted;
+
+__global__ void spmm_assume_sorted_kernel() { spmm_sorted = 1; }
+
+__global__ void spmm_check_sorted_kernel(const int32_t *__restrict__ row_offsets,
+                                         const int32_t *__restrict__ column_indices, int64_t rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  bool ascending = true;
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const int start = row_offsets[row], stop = row_offsets[row + 1];
+    for (int i = start + lane; i + 1 < stop; i += 32)
+      ascending &= column_indices[i] <= column_indices[i + 1];
+  }
+  if (!ascending) spmm_sorted = 0;
+}
 
 __global__ void __launch_bounds__(kBulkWarps * 32, 1)
 csr_spmm_bulk_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
                      const float *__restrict__ values, const float *__restrict__ dense,
                      float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
-                     int64_t output_pitch) {
+                     int64_t output_pitch, int column_lo, int column_hi, int phase, int phases) {
   extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const bool accumulate = phase > 0;
+  if (phases > 1 && !spmm_sorted) {  // some row is not ascending: do everything in launch 0
+    if (phase > 0) return;
+    column_lo = INT32_MIN;
+    column_hi = INT32_MAX;
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int feature0 = blockIdx.y * 128;
   const int width = min(128, features - feature0);         // features of this chunk
@@ -141,118 +173,229 @@ csr_spmm_bulk_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__r
   }
   __syncwarp();
 
+  // This warp's rows are first_row, first_row + warps, ...; `count` of them.
   const int64_t warps = (int64_t)gridDim.x * kBulkWarps;
-  int64_t row = (int64_t)blockIdx.x * kBulkWarps + warp;
-  if (row >= rows) return;
+  const int64_t first_row = (int64_t)blockIdx.x * kBulkWarps + warp;
+  if (first_row >= rows) return;
+  const int64_t count = (rows - first_row + warps - 1) / warps;
   const float *source = dense + feature0;
 
-  // Requests the gathers of one batch into `stage`; lane j copies non-zero j's row of X.
-  auto request = [&](int stage, int base, int stop) -> Batch {
-    Batch batch;
-    batch.count = max(0, min(32, stop - base));
-    batch.column = 0;
-    batch.value = 0.0f;
-    if (lane < batch.count) {
-      batch.column = __ldcs(column_indices + base + lane);
-      batch.value = __ldcs(values + base + lane);
+  // A batch is up to 32 consecutive non-zeros of one row.  The walk over batches is a
+  // three-deep software pipeline, so no memory round trip sits on the critical path:
+  //   offsets   of 32 of this warp's rows at a time (lane k holds the k-th of them),
+  //   indices   (column, value) of the batch after the next one,
+  //   copies    of the next batch, while the current one is folded.
+  struct Cursor {
+    int64_t ordinal;   // which of this warp's rows
+    int base, stop;    // batch = non-zeros [base, min(base + 32, stop))
+  };
+  int cached_start = 0, cached_stop = 0;  // lane k: offsets of row ordinal (cache_block * 32 + k)
+  int64_t cache_block = -1;
+  auto offsets_of = [&](int64_t ordinal, int *start, int *stop) {
+    if (ordinal / 32 != cache_block) {
+      cache_block = ordinal / 32;
+      const int64_t mine = cache_block * 32 + lane;
+      cached_start = cached_stop = 0;
+      if (mine < count) {
+        const int64_t r = first_row + mine * warps;
+        cached_start = __ldg(row_offsets + r);
+        cached_stop = __ldg(row_offsets + r + 1);
+      }
     }
+    *start = __shfl_sync(0xffffffffu, cached_start, (int)(ordinal % 32));
+    *stop = __shfl_sync(0xffffffffu, cached_stop, (int)(ordinal % 32));
+  };
+  struct Batch {
+    int column;        // lane j <-> j-th non-zero of the batch
+    float value;
+    int64_t row;       // -1: no batch (past the end)
+    int base, stop;
+    bool first, last;  // first / last batch of its row
+  };
+  auto advance = [&](Cursor &c) -> bool {   // false when the warp's rows are exhausted
+    if (c.base + 32 < c.stop) { c.base += 32; return true; }
+    if (++c.ordinal >= count) return false;
+    offsets_of(c.ordinal, &c.base, &c.stop);
+    return true;
+  };
+  auto fetch = [&](const Cursor &c, bool valid, bool first) -> Batch {
+    Batch b;
+    b.row = valid ? first_row + c.ordinal * warps : -1;
+    b.base = c.base; b.stop = c.stop; b.first = first; b.last = c.base + 32 >= c.stop;
+    b.column = 0; b.value = 0.0f;
+    if (valid && c.base + lane < c.stop) {
+      b.column = __ldcs(column_indices + c.base + lane);
+      b.value = __ldcs(values + c.base + lane);
+    }
+    return b;
+  };
+  // Requests the gathers of one batch into `stage`; returns the lanes that take part.
+  auto request = [&](const Batch &b, int stage) -> unsigned {
+    const bool mine = b.row >= 0 && b.base + lane < b.stop && b.column >= column_lo && b.column < column_hi;
+    const unsigned mask = __ballot_sync(0xffffffffu, mine);
     const uint32_t bar = shared_address(bars + stage);
-    if (lane == 0 && batch.count > 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(batch.count * row_bytes)
+    if (lane == 0 && mask != 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(__popc(mask) * row_bytes)
                    : "memory");
     __syncwarp();
-    if (lane < batch.count) {
-      const float *from = source + (int64_t)batch.column * dense_pitch;
+    if (mine) {
+      const float *from = source + (int64_t)b.column * dense_pitch;
       const uint32_t to = shared_address(stage_base + stage * kBulkStageBytes + lane * kBulkRowBytes);
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                    ::"r"(to), "l"(from), "r"(row_bytes), "r"(bar)
                    : "memory");
     }
-    return batch;
+    return mask;
+  };
+  auto try_wait = [&](int stage, uint32_t parity) -> bool {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(shared_address(bars + stage)), "r"(parity) : "memory");
+    return done != 0;
   };
 
-  int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
+  Cursor cursor{0, 0, 0};
+  offsets_of(0, &cursor.base, &cursor.stop);
+  Batch current = fetch(cursor, true, true);
+  bool more = true;
+  bool crossed;
+  { const int64_t before = cursor.ordinal; more = advance(cursor); crossed = cursor.ordinal != before; }
+  Batch next = fetch(cursor, more, crossed);
+  uint32_t parity0 = 0, parity1 = 0;
   int stage = 0;
-  uint32_t parity[kBulkStages];
-#pragma unroll
-  for (int s = 0; s < kBulkStages; ++s) parity[s] = 0;
-  int base = start;
-  Batch current = request(stage, base, stop);
-  bool alive = true;
-  while (alive) {
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    int64_t next_row = row + warps;
-    while (true) {
-      // what comes after the current batch: the rest of this row, or the first batch of the next row
-      const bool more_in_row = base + 32 < stop;
-      int following_start = 0, following_stop = 0;
-      const bool has_following = more_in_row || next_row < rows;
-      if (more_in_row) {
-        following_start = base + 32;
-        following_stop = stop;
-      } else if (next_row < rows) {
-        following_start = __ldg(row_offsets + next_row);
-        following_stop = __ldg(row_offsets + next_row + 1);
-      }
-      const int other = (stage + 1) % kBulkStages;
-      Batch following;
-      following.count = 0; following.column = 0; following.value = 0.0f;
-      if (has_following) following = request(other, following_start, following_stop);
+  unsigned current_mask = request(current, stage);
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  while (current.row >= 0) {
+    // indices of the batch after next, then the copies of the next batch
+    Batch after;
+    {
+      const int64_t before = cursor.ordinal;
+      if (more) more = advance(cursor);
+      after = fetch(cursor, more, cursor.ordinal != before);
+    }
+    const unsigned next_mask = request(next, stage ^ 1);
 
-      if (current.count > 0) {
-        const uint32_t bar = shared_address(bars + stage);
-        uint32_t done = 0;
-        const long long begin = clock64();
-        while (true) {
-          asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                       : "=r"(done) : "r"(bar), "r"(parity[stage]) : "memory");
-          if (done) break;
-          if (clock64() - begin > kBulkWaitCycles) break;
+    if (current.first) {
+      acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (accumulate && active)  // partial sums of the earlier column blocks
+        acc = __ldcs(reinterpret_cast<const float4 *>(output + current.row * output_pitch + feature0 + lane * 4));
+    }
+    if (current_mask != 0) {
+      const uint32_t parity = stage ? parity1 : parity0;
+      const long long begin = clock64();
+      bool landed = try_wait(stage, parity);
+      while (!landed && clock64() - begin < kBulkWaitCycles) landed = try_wait(stage, parity);
+      if (!landed) {  // give up: flag the failure, leave the row unwritten and stop this warp
+        if (lane == 0 && atomicCAS(&spmm_status[0], 0, 1) == 0) spmm_status[1] = (int)current.row;
+        if (next_mask != 0) {  // let the batch already requested land before the buffers go away
+          const long long drain = clock64();
+          const uint32_t other_parity = stage ? parity0 : parity1;
+          while (!try_wait(stage ^ 1, other_parity) && clock64() - drain < kBulkWaitCycles / 8) {}
         }
-        if (!done) {  // give up: flag the failure, leave the row unwritten and stop this warp
-          if (lane == 0 && atomicCAS(&spmm_status[0], 0, 1) == 0) spmm_status[1] = (int)row;
-          if (following.count > 0) {  // let the batch already requested land before the buffers go away
-            const uint32_t other_bar = shared_address(bars + other);
-            const long long drain = clock64();
-            uint32_t landed = 0;
-            while (!landed && clock64() - drain < kBulkWaitCycles / 8)
-              asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                           : "=r"(landed) : "r"(other_bar), "r"(parity[other]) : "memory");
-          }
-          alive = false;
-          break;
-        }
-        parity[stage] ^= 1;
-        const unsigned char *staged = stage_base + stage * kBulkStageBytes + lane * 16;
+        return;
+      }
+      if (stage) parity1 ^= 1; else parity0 ^= 1;
+      const unsigned char *staged = stage_base + stage * kBulkStageBytes + lane * 16;
 #pragma unroll 8
-        for (int j = 0; j < 32; ++j) {
-          const float weight = __shfl_sync(0xffffffffu, current.value, j);
-          if (active && j < current.count) {
-            const float4 x = *reinterpret_cast<const float4 *>(staged + j * kBulkRowBytes);
-            acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x.x));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x.z));
-            acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x.w));
-          }
+      for (int j = 0; j < 32; ++j) {
+        const float weight = __shfl_sync(0xffffffffu, current.value, j);
+        if (active && ((current_mask >> j) & 1u)) {
+          const float4 x = *reinterpret_cast<const float4 *>(staged + j * kBulkRowBytes);
+          acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x.x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x.y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x.z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x.w));
         }
-        __syncwarp();  // every lane has read the stage before it is requested again
       }
-      stage = other;
-      current = following;
-      if (more_in_row) {
-        base += 32;
-        continue;
+      __syncwarp();  // every lane has read the stage before it is requested again
+    }
+    if (current.last && active)
+      __stcs(reinterpret_cast<float4 *>(output + current.row * output_pitch + feature0 + lane * 4), acc);
+    stage ^= 1;
+    current = next;
+    current_mask = next_mask;
+    next = after;
+  }
+  // No copy is left in flight here: every requested batch was waited for.
+}
+
+// Column-blocked launches see only a few non-zeros per row and mostly hit L2, where
+// round trips are short: there the gathers are kept in registers (eight in flight per
+// lane) and rows are spread over many warps instead of being staged through shared memory.
+constexpr int kBlockWarps = 8;
+
+__global__ void __launch_bounds__(kBlockWarps * 32)
+csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
+                      const float *__restrict__ values, const float *__restrict__ dense,
+                      float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
+                      int64_t output_pitch, int column_lo, int column_hi, int phase) {
+  const bool accumulate = phase > 0;
+  if (!spmm_sorted) {  // some row is not ascending: launch 0 covers every column
+    if (phase > 0) return;
+    column_lo = INT32_MIN;
+    column_hi = INT32_MAX;
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kBlockWarps + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int feature = blockIdx.y * 128 + lane * 4;
+  const bool active = feature < features;
+  const int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float *destination = output + row * output_pitch + feature;
+  if (accumulate && active) acc = __ldcs(reinterpret_cast<const float4 *>(destination));
+  const float *source = dense + feature;
+  bool touched = !accumulate;  // launch 0 always writes (rows without a term in the block become 0)
+  for (int base = start; base < stop; base += 32) {
+    int column = 0;
+    float value = 0.0f;
+    bool mine = false;
+    if (base + lane < stop) {
+      column = __ldcs(column_indices + base + lane);
+      value = __ldcs(values + base + lane);
+      mine = column >= column_lo && column < column_hi;
+    }
+    unsigned mask = __ballot_sync(0xffffffffu, mine);
+    touched |= mask != 0;
+    while (mask != 0) {  // eight gathers at a time, in storage order
+      int lanes[8];
+      float4 gathered[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        lanes[u] = mask ? __ffs(mask) - 1 : -1;
+        if (mask) mask &= mask - 1;
+        const int c = __shfl_sync(0xffffffffu, column, lanes[u] < 0 ? 0 : lanes[u]);
+        if (active && lanes[u] >= 0)
+          gathered[u] = __ldg(reinterpret_cast<const float4 *>(source + (int64_t)c * dense_pitch));
       }
-      if (active) __stcs(reinterpret_cast<float4 *>(output + row * output_pitch + feature0 + lane * 4), acc);
-      if (next_row >= rows) alive = false;
-      row = next_row;
-      start = following_start;
-      stop = following_stop;
-      base = start;
-      break;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float weight = __shfl_sync(0xffffffffu, value, lanes[u] < 0 ? 0 : lanes[u]);
+        if (active && lanes[u] >= 0) {
+          acc.x = __fadd_rn(acc.x, __fmul_rn(weight, gathered[u].x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(weight, gathered[u].y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(weight, gathered[u].z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(weight, gathered[u].w));
+        }
+      }
     }
   }
-  // No copy is left in flight here on the normal path: every requested batch was waited for.
+  if (active && touched) __stcs(reinterpret_cast<float4 *>(destination), acc);
+}
+
+// Number of column blocks: X is cut into slices of at most kBlockBytes so that a slice
+// stays resident in L2 (126 MB, shared with the streamed index, value and Y traffic).
+constexpr int64_t kBlockBytes = 72ll << 20;
+int column_phases(int64_t columns, int64_t features) {
+  static const int forced = [] {
+    const char *text = getenv("INTENT_B200_SPMM_PHASES");  // tuning override, 1..16
+    const int value = text ? atoi(text) : 0;
+    return value >= 1 && value <= 16 ? value : 0;
+  }();
+  if (forced) return forced;
+  const int64_t bytes = columns * features * 4;
+  const int64_t phases = (bytes + kBlockBytes - 1) / kBlockBytes;
+  return (int)(phases < 1 ? 1 : phases > 8 ? 8 : phases);
 }
 
 // result[0] = first bad position + 1 (0 = valid); atomicMin over positions.
@@ -311,9 +454,27 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
     const int64_t wanted = (rows + kBulkWarps - 1) / kBulkWarps;
     const int64_t resident = sm_count();
     const dim3 grid((unsigned)(wanted < resident ? wanted : resident), (unsigned)((x_d1 + 127) / 128));
-    csr_spmm_bulk_kernel<<<grid, kBulkWarps * 32, kBulkSmemBytes, s>>>(
-        (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
-        (const float *)dense, (float *)output, rows, (int)x_d1, x_s0, y_s0);
+    const int phases = column_phases(x_d0, x_d1);
+    if (phases > 1) {
+      spmm_assume_sorted_kernel<<<1, 1, 0, s>>>();
+      spmm_check_sorted_kernel<<<sm_count() * 4, 256, 0, s>>>((const int32_t *)row_offsets,
+                                                             (const int32_t *)column_indices, rows);
+    }
+    const int64_t block = (x_d0 + phases - 1) / phases;
+    const dim3 block_grid((unsigned)((rows + kBlockWarps - 1) / kBlockWarps), grid.y);
+    for (int phase = 0; phase < phases; ++phase) {
+      const int64_t lo = phase * block, hi = (phase + 1 == phases) ? (int64_t)INT32_MAX : (phase + 1) * block;
+      if (phases > 1) {
+        csr_spmm_block_kernel<<<block_grid, kBlockWarps * 32, 0, s>>>(
+            (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
+            (const float *)dense, (float *)output, rows, (int)x_d1, x_s0, y_s0, (int)lo, (int)hi, phase);
+        continue;
+      }
+      csr_spmm_bulk_kernel<<<grid, kBulkWarps * 32, kBulkSmemBytes, s>>>(
+          (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
+          (const float *)dense, (float *)output, rows, (int)x_d1, x_s0, y_s0,
+          phases > 1 ? (int)lo : INT32_MIN, phases > 1 ? (int)hi : INT32_MAX, phase, phases);
+    }
   } else
     csr_spmm_kernel<false><<<(unsigned)ctas, kWarpsPerCta * 32, 0, s>>>(
         (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,

@@ -47,8 +47,12 @@ def test_gemm_8192_cubed():
     oracle.gemm(a, b, rows=rows, out=expected)
     block = slice(rows[0], rows[0] + rows[1])
     assert relative_error(c[block], expected[block]) <= 1e-2
-    # linearity in exact arithmetic: doubling A doubles C bit for bit (power-of-two scale)
-    assert torch.equal(ops.gemm((ad * 2).contiguous(), bd).float(), c.float() * 2)
+    # linearity in exact arithmetic: doubling A doubles C bit for bit (a power-of-two scale commutes
+    # with f16 rounding except where C is subnormal in f16)
+    doubled = ops.gemm((ad * 2).contiguous(), bd).float()
+    normal = c.float().abs() >= 2.0 ** -13
+    assert torch.equal(doubled[normal], c.float()[normal] * 2)
+    assert (doubled[~normal] - c.float()[~normal] * 2).abs().max() <= 2.0 ** -23
     # checksum of checksums: sum_n C[m, n] == A[m, :] . sum_n B[:, n] within accumulation tolerance
     column_sums = bd.double().sum(dim=1)
     assert relative_error(c.double().sum(dim=1), ad.double() @ column_sums) <= 2e-3
