@@ -478,7 +478,18 @@ def main() -> None:
     distributed = world > 1
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.distributed.init_process_group("nccl", device_id=device)
+        # NCCL prints its version banner on stdout at the first collective; stdout carries the
+        # one JSON line only, so the banner is sent to stderr.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            torch.distributed.init_process_group("nccl", device_id=device)
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     from intent_b200 import _native
     _native.library()                                     # fail loudly if the CUDA extension is missing
     peak_table, peak_kind = peaks()

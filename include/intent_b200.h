@@ -98,9 +98,9 @@ int b200_layer_norm(const void *x, int64_t x_d0, int64_t x_d1, int64_t x_s0, int
  * tcgen05 tensor cores.  Replaces gemm (ACTIVATION NONE / RELU) and bf16_gemm
  * (python/intent/examples/kernels/contraction/gemm.py:54-92).
  * a is (M,K), b is (K,N), c is (M,N) in element strides.  Accepted layouts:
- * a K-major (a_s1 == 1), b K-major (b_s0 == 1, "column-major B") or N-major
- * (b_s1 == 1), c row-major (c_s1 == 1); leading strides multiples of 8
- * elements and 16-byte aligned bases (TMA requirements).
+ * a K-major (a_s1 == 1); b K-major (b_s0 == 1, "column-major B") or N-major
+ * (b_s1 == 1, plain row-major (K,N)); c row-major (c_s1 == 1); leading strides
+ * multiples of 8 elements and 16-byte aligned bases (TMA requirements).
  * workspace: B200_WORKSPACE_WORDS int32 words, zeroed once by the caller.
  */
 int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a_s1,
@@ -154,7 +154,7 @@ int b200_gemm_static_scratch(const void *a, int64_t a_d0, int64_t a_d1, int64_t 
  * query head / head_group.  exp2 and the final reciprocal use
  * ex2.approx.ftz / div.approx.ftz as the reference's NVIDIA target does
  * (lib/Target/NVIDIA/IR/Target.cpp:62-86).  Requires unit innermost strides,
- * D == DV == 128, other strides positive multiples of 8 elements, 16-byte
+ * D == DV in {64, 128}, other strides positive multiples of 8 elements, 16-byte
  * aligned bases and scale > 0.  An empty key sequence yields zeros.
  */
 int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,

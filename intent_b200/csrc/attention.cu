@@ -1,4 +1,4 @@
-// Flash-attention forward on the tcgen05 tensor cores (bf16 / f16, head dim 128).
+// Flash-attention forward on the tcgen05 tensor cores (bf16 / f16, head dim 64 or 128).
 //
 // One CTA per SM owns TWO tiles of 128 query rows (A and B, 256 consecutive rows
 // of one (batch, head)) and streams the key/value sequence through them in tiles
@@ -38,11 +38,11 @@ namespace {
 
 constexpr int kBlockM = 128;                     // query rows per tile (two tiles per CTA)
 constexpr int kBlockN = 128;
-constexpr int kHeadDim = 128;
+constexpr int kMaxHeadDim = 128;                 // head dimension is a template parameter: 64 or 128
 constexpr int kThreads = 320;
 constexpr int kTmemColumns = 512;
 constexpr int kRingSlots = 5;
-constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one Q / K / V tile
+constexpr uint32_t kTileBytes = 128 * 128 * 2;   // shared-memory slot of one Q / K / V tile (half used at head dim 64)
 constexpr uint32_t kHalfBytes = kTileBytes / 2;  // 64-column half
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
@@ -91,7 +91,7 @@ struct RingPosition {
   __device__ explicit RingPosition(int index) : slot(index % kRingSlots), phase((index / kRingSlots) & 1) {}
 };
 
-template <typename T>
+template <typename T, int kHeadDim>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const Shape shape, int *status) {
@@ -102,6 +102,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   unsigned char *ring = tiles + 2 * kTileBytes;         // kRingSlots tiles
   Barriers *bars = reinterpret_cast<Barriers *>(tiles + (2 + kRingSlots) * kTileBytes);
 
+  constexpr uint32_t kLoadBytes = 128 * kHeadDim * 2;  // bytes TMA delivers per tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heaviest query tiles (most key tiles under the causal mask) are scheduled first
   const int pairs = (shape.seq_q + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -145,11 +146,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (tc::elect_one()) {
-      tc::mbar_expect_tx(&bars->q_full, 2 * kTileBytes);
+      tc::mbar_expect_tx(&bars->q_full, 2 * kLoadBytes);
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
         tc::tma_load_4d(q_tiles + x * kTileBytes, &map_q, &bars->q_full, 0, q0 + x * kBlockM, head, batch);
-        tc::tma_load_4d(q_tiles + x * kTileBytes + kHalfBytes, &map_q, &bars->q_full, 64, q0 + x * kBlockM, head, batch);
+        if (kHeadDim > 64)
+          tc::tma_load_4d(q_tiles + x * kTileBytes + kHalfBytes, &map_q, &bars->q_full, 64, q0 + x * kBlockM, head, batch);
       }
       int issued = 0;
       bool alive = true;
@@ -162,9 +164,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         unsigned char *slot = ring + at.slot * kTileBytes;
         const CUtensorMap *map = (index & 1) ? &map_v : &map_k;
         const int key0 = (index >> 1) * kBlockN;
-        tc::mbar_expect_tx(&bars->slot_full[at.slot], kTileBytes);
+        tc::mbar_expect_tx(&bars->slot_full[at.slot], kLoadBytes);
         tc::tma_load_4d(slot, map, &bars->slot_full[at.slot], 0, key0, kv_head, batch);
-        tc::tma_load_4d(slot + kHalfBytes, map, &bars->slot_full[at.slot], 64, key0, kv_head, batch);
+        if (kHeadDim > 64) tc::tma_load_4d(slot + kHalfBytes, map, &bars->slot_full[at.slot], 64, key0, kv_head, batch);
         ++issued;
       }
       if (!alive) {
@@ -206,7 +208,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // A: 16 keys = 8 packed TMEM columns; B: 16 key rows = 2048 bytes further down the V tile
-          tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kHeadDim, tmem_base + x * kBlockN + kk * 8,
+          tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kMaxHeadDim, tmem_base + x * kBlockN + kk * 8,
                          tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes), idesc_o, (j | kk) != 0);
         }
         if (j == tiles_of[x] - 1) tc::mma_commit(&bars->o_full[x]);
@@ -244,7 +246,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int q_row = tile_q0 + row_in_tile;
     const int my_tiles = tiles_of[x];
     const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
-    const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kHeadDim;
+    const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
     float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
     float sum = 0.0f;
     bool alive = true;
@@ -384,7 +386,7 @@ int tensor_map_4d(CUtensorMap *map, const void *base, int64_t d0, int64_t d1, in
   return encode_tensor_map_16bit(map, base, 4, dims, strides, box, true);
 }
 
-template <typename T>
+template <typename T, int kHeadDim>
 int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd, const int64_t *qs,
                     const int64_t *kd, const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
                     int head_group, int causal, int *status, cudaStream_t stream) {
@@ -402,7 +404,7 @@ int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd,
   if (result != B200_OK) return result;
   result = tensor_map_4d(&map_v, v, batch, heads_k, seq_k, kHeadDim, vs[0], vs[1], vs[2]);
   if (result != B200_OK) return result;
-  auto kernel = attention_kernel<T>;
+  auto kernel = attention_kernel<T, kHeadDim>;
   static std::once_flag configured;
   cudaError_t attribute_error = cudaSuccess;
   std::call_once(configured, [&] {
@@ -448,8 +450,8 @@ extern "C" int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, i
   if (qd[0] == 0 || qd[1] == 0 || qd[2] == 0) return B200_OK;
   if (dtype != B200_F16 && dtype != B200_BF16)
     return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: element type %d is not f16/bf16", dtype);
-  if (qd[3] != kHeadDim || vd[3] != kHeadDim)
-    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: head dimensions must be 128 (got D=%lld, DV=%lld)",
+  if (qd[3] != vd[3] || (qd[3] != 64 && qd[3] != 128))
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: head dimensions must be D == DV in {64, 128} (got D=%lld, DV=%lld)",
                 (long long)qd[3], (long long)vd[3]);
   if (!q || !k || !v || !o) return fail(B200_ERR_INVALID_ARGUMENT, "flash_attention: null buffer");
   if (!workspace || ws_d0 < B200_WORKSPACE_WORDS || (ws_d0 > 1 && ws_s0 != 1))
@@ -468,10 +470,10 @@ extern "C" int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, i
   if (qd[2] > INT32_MAX - 256 || kd[2] > INT32_MAX - 256 || qd[1] > 65535 || qd[0] > 65535)
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "flash_attention: extent exceeds the launch limits");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_F16)
-    return attention_typed<__half>((const __half *)q, (const __half *)k, (const __half *)v, (__half *)o, qd, qs, kd, ks,
-                                   vs, os, scale, head_group, causal, (int *)workspace, s);
-  return attention_typed<__nv_bfloat16>((const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v,
-                                        (__nv_bfloat16 *)o, qd, qs, kd, ks, vs, os, scale, head_group, causal,
-                                        (int *)workspace, s);
+#define B200_ATTENTION(T, D)                                                                                    \
+  attention_typed<T, D>((const T *)q, (const T *)k, (const T *)v, (T *)o, qd, qs, kd, ks, vs, os, scale, head_group, \
+                        causal, (int *)workspace, s)
+  if (dtype == B200_F16) return qd[3] == 64 ? B200_ATTENTION(__half, 64) : B200_ATTENTION(__half, 128);
+  return qd[3] == 64 ? B200_ATTENTION(__nv_bfloat16, 64) : B200_ATTENTION(__nv_bfloat16, 128);
+#undef B200_ATTENTION
 }

@@ -38,6 +38,7 @@ constexpr int kEpilogueThreads = 128;
 constexpr uint32_t kBytesA = kBlockM * kBlockK * 2;
 constexpr uint32_t kBytesB = kBlockN * kBlockK * 2;
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kChunkBytesB = 64 * kBlockK * 2;  // one 64-column chunk of an N-major B stage
 
 struct __align__(8) Barriers {
   uint64_t full[kStages];
@@ -74,7 +75,9 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-template <typename T, bool RELU>
+// B_N_MAJOR: B is stored with N contiguous (row-major (K,N)); its stage is then four
+// boxes of 64 N-columns x 64 K-rows (8 KB each) and the MMA reads it as an MN-major operand.
+template <typename T, bool RELU, bool B_N_MAJOR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             T *__restrict__ c, int64_t c_pitch, int m, int n, int k, int *status) {
@@ -129,7 +132,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           unsigned char *slot = tiles + stage * kStageBytes;
           tc::mbar_expect_tx(&bars->full[stage], kStageBytes);
           tc::tma_load_2d(slot, &map_a, &bars->full[stage], kb * kBlockK, tm * kBlockM);
-          tc::tma_load_2d(slot + kBytesA, &map_b, &bars->full[stage], kb * kBlockK, tn * kBlockN);
+          if (B_N_MAJOR) {
+#pragma unroll
+            for (int chunk = 0; chunk < kBlockN / 64; ++chunk)
+              tc::tma_load_2d(slot + kBytesA + chunk * kChunkBytesB, &map_b, &bars->full[stage],
+                              tn * kBlockN + chunk * 64, kb * kBlockK);
+          } else {
+            tc::tma_load_2d(slot + kBytesA, &map_b, &bars->full[stage], kb * kBlockK, tn * kBlockN);
+          }
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -149,7 +159,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ----------------------------------------------------------- MMA issuer
     if (tc::elect_one()) {
       constexpr uint32_t idesc = tc::instr_desc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
-                                                    kBlockM, kBlockN);
+                                                    kBlockM, kBlockN, B_N_MAJOR);
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool alive = true;
@@ -169,7 +179,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // +32 bytes per K step inside the swizzle span = +2 in 16-byte units
-            tc::mma_f16_ss(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
+            if (B_N_MAJOR)  // 16 K-rows of 128 bytes further down every 64-column chunk
+              tc::mma_f16_ss(tmem_d, desc_a + 2 * kk,
+                             tc::smem_desc_mn_major_sw128(a_address + kBytesA + kk * 2048, kChunkBytesB), idesc,
+                             (kb | kk) != 0);
+            else
+              tc::mma_f16_ss(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
           }
           tc::mma_commit(&bars->empty[stage]);  // frees the ring slot when these MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -285,7 +300,7 @@ int cached_map_2d(CUtensorMap *out, const void *base, uint64_t inner, uint64_t o
 
 template <typename T>
 int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, int64_t a_pitch,
-               int64_t b_pitch, int64_t c_pitch, int relu, int *status, cudaStream_t stream) {
+               int64_t b_pitch, int64_t c_pitch, int relu, bool b_n_major, int *status, cudaStream_t stream) {
   if (k == 0) {
     zero_fill_kernel<T><<<sm_count() * 4, 256, 0, stream>>>(c, c_pitch, (int)m, (int)n);
     B200_CUDA_TRY(cudaGetLastError());
@@ -294,12 +309,15 @@ int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, in
   CUtensorMap map_a, map_b;
   int result = cached_map_2d(&map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)a_pitch * 2, kBlockK, kBlockM);
   if (result != B200_OK) return result;
-  result = cached_map_2d(&map_b, b, (uint64_t)k, (uint64_t)n, (uint64_t)b_pitch * 2, kBlockK, kBlockN);
+  result = b_n_major
+      ? cached_map_2d(&map_b, b, (uint64_t)n, (uint64_t)k, (uint64_t)b_pitch * 2, 64, kBlockK)
+      : cached_map_2d(&map_b, b, (uint64_t)k, (uint64_t)n, (uint64_t)b_pitch * 2, kBlockK, kBlockN);
   if (result != B200_OK) return result;
-  auto kernel = relu ? gemm_kernel<T, true> : gemm_kernel<T, false>;
-  static std::once_flag configured[4];
+  auto kernel = b_n_major ? (relu ? gemm_kernel<T, true, true> : gemm_kernel<T, false, true>)
+                          : (relu ? gemm_kernel<T, true, false> : gemm_kernel<T, false, false>);
+  static std::once_flag configured[8];
   cudaError_t attribute_error = cudaSuccess;
-  std::call_once(configured[(std::is_same<T, __half>::value ? 0 : 2) + (relu ? 1 : 0)], [&] {
+  std::call_once(configured[(std::is_same<T, __half>::value ? 0 : 4) + (relu ? 1 : 0) + (b_n_major ? 2 : 0)], [&] {
     attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   });
   B200_CUDA_TRY(attribute_error);
@@ -359,21 +377,26 @@ extern "C" int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0
     return fail(B200_ERR_INVALID_ARGUMENT, "gemm: element type %d is not f16/bf16", dtype);
   if (n > 1 && c_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: c must be row-major (c_s1 == 1)");
   if (k > 1 && a_s1 != 1) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: a must be K-major (a_s1 == 1)");
-  if (k > 1 && b_s0 != 1)
-    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: b must be K-major (b_s0 == 1, i.e. column-major (K,N))");
+  // B: K-major (b_s0 == 1, "column-major (K,N)") or N-major (b_s1 == 1, row-major (K,N))
+  const bool b_k_major = k <= 1 || b_s0 == 1;
+  const bool b_n_major = !b_k_major && (n <= 1 || b_s1 == 1);
+  if (!b_k_major && !b_n_major)
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: b needs a unit stride along K (b_s0 == 1) or along N (b_s1 == 1)");
   if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gemm: extent exceeds int32");
   // a 1-row / 1-column operand has a free leading stride; give TMA a legal one
   const int64_t a_pitch = m > 1 ? a_s0 : (k + 7) / 8 * 8;
-  const int64_t b_pitch = n > 1 ? b_s1 : (k + 7) / 8 * 8;
-  if (k > 0 && (a_pitch % 8 || b_pitch % 8 || a_pitch < k || b_pitch < k || !aligned16(a) || !aligned16(b)))
+  const int64_t b_pitch = b_n_major ? (k > 1 ? b_s0 : (n + 7) / 8 * 8) : (n > 1 ? b_s1 : (k + 7) / 8 * 8);
+  const int64_t b_inner = b_n_major ? n : k;
+  if (k > 0 && (a_pitch % 8 || b_pitch % 8 || a_pitch < k || b_pitch < b_inner || !aligned16(a) || !aligned16(b)))
     return fail(B200_ERR_UNSUPPORTED_LAYOUT,
-                "gemm: TMA needs 16-byte aligned bases and leading strides that are multiples of 8 elements and >= K");
+                "gemm: TMA needs 16-byte aligned bases and leading strides that are multiples of 8 elements and "
+                "cover the contiguous extent");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == B200_F16)
     return gemm_typed<__half>((const __half *)a, (const __half *)b, (__half *)c, m, n, k, a_pitch, b_pitch, c_s0,
-                              relu, (int *)workspace, s);
+                              relu, b_n_major, (int *)workspace, s);
   return gemm_typed<__nv_bfloat16>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)c, m, n, k,
-                                   a_pitch, b_pitch, c_s0, relu, (int *)workspace, s);
+                                   a_pitch, b_pitch, c_s0, relu, b_n_major, (int *)workspace, s);
 }
 
 // ---------------------------------------------------------------------------

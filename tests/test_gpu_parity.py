@@ -98,9 +98,21 @@ def test_gemm_relu_empty_k_and_layout_errors():
                      torch.empty(0, 16, dtype=torch.float16, device=DEV))
     assert empty.shape == (8, 16) and not empty.any()
     with pytest.raises(NotImplementedError):
-        ops.gemm(a.to(DEV), b.contiguous().to(DEV))                # N-major B is not accepted
+        ops.gemm(a.to(DEV).t().contiguous().t(), b.to(DEV))        # A must be K-major
     with pytest.raises(ValueError):
         ops.gemm(a.to(DEV), b[:-8].to(DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(128, 192, 256), (300, 520, 1000), (64, 8, 64), (1024, 1024, 512)])
+def test_gemm_row_major_b(dtype, m, n, k):
+    """b given as a plain contiguous (K, N) tensor, the layout of the reference's own gemm program
+    (python/intent/examples/programs/matrix.py:14-18)."""
+    a, b = workloads.gemm_inputs(m, n, k, seed=n, dtype=dtype)
+    b = b.contiguous()
+    c = ops.gemm(a.to(DEV), b.to(DEV))
+    ops.workspace_status(DEV)
+    assert relative_error(c, oracle.gemm(a, b)) <= 1e-2
 
 
 def test_gemm_is_linear_in_a():
@@ -137,8 +149,21 @@ def test_flash_attention_gqa_noncausal_and_rectangular():
     ops.workspace_status(DEV)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_flash_attention_head_dimension_64(dtype):
+    """The shape of the reference's registered attention program
+    (python/intent/examples/programs/streaming.py:15-21): bf16, GQA 4, causal, D = 64."""
+    q, k, v, scale = workloads.attention_inputs(2, 8, 256, 64, seed=3, dtype=dtype, kv_heads=2)
+    out = ops.flash_attention(*cuda(q, k, v), scale, head_group=4)
+    ops.workspace_status(DEV)
+    assert relative_error(out, oracle.attention(q, k, v, scale, head_group=4)) <= 1e-2
+    q, k, v, scale = workloads.attention_inputs(1, 2, 700, 64, seed=4, dtype=dtype)
+    out = ops.flash_attention(*cuda(q, k, v), scale, causal=False)
+    assert relative_error(out, oracle.attention(q, k, v, scale, causal=False)) <= 1e-2
+
+
 def test_flash_attention_refuses_other_head_dimensions():
-    q, k, v, scale = workloads.attention_inputs(1, 2, 64, 64, seed=3)
+    q, k, v, scale = workloads.attention_inputs(1, 2, 64, 32, seed=3)
     with pytest.raises(NotImplementedError, match="head dimensions"):
         ops.flash_attention(*cuda(q, k, v), scale)
 

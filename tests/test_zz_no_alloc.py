@@ -50,7 +50,7 @@ def test_it_validates_like_the_allocating_entry():
     a, b = workloads.gemm_inputs(64, 64, 64, seed=3)
     a, b = a.to(DEV), b.t().contiguous().to(DEV).t()
     with pytest.raises(NotImplementedError):
-        static_scratch_gemm(a, b.contiguous())               # N-major B
+        static_scratch_gemm(a, b.contiguous())               # this entry takes K-major B only
     with pytest.raises(ValueError):
         static_scratch_gemm(a, b[:-8])                       # K mismatch
     empty = static_scratch_gemm(a[:, :0], b[:0])
