@@ -47,8 +47,8 @@ NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/ (null where no capture of that kernel exists yet).
-NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221000448, "gemm": 1149760712, "attention": 1056682240,
-                     "spmm": 1968709184}
+NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1059080448,
+                     "spmm": 975351808}
 
 
 def peaks() -> tuple[dict, str]:

@@ -126,25 +126,14 @@ __device__ __forceinline__ uint32_t shared_address(const void *pointer) {
 // block of columns small enough to (mostly) stay in L2: launch p adds the terms whose
 // column lies in block p to Y (read-modify-write, streamed).  With ascending
 // columns inside every row the blocks are visited in storage order, so the sum
-// of a row is still accumulated strictly left to right.  `spmm_sorted` is set by
-// a check pass at the start of the call; if some row is not ascending, launch 0
-// covers every column and the other launches return at once.
+// of a row is still accumulated strictly left to right.  Launch 0 reads every
+// column index anyway, so it also checks that rows ascend and clears `spmm_sorted`
+// if one does not; launch 1 then recomputes Y from scratch over all columns (in
+// storage order) and the remaining launches return at once.
 __device__ int spmm_sorted;
 
 __global__ void spmm_assume_sorted_kernel() { spmm_sorted = 1; }
 
-__global__ void spmm_check_sorted_kernel(const int32_t *__restrict__ row_offsets,
-                                         const int32_t *__restrict__ column_indices, int64_t rows) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  bool ascending = true;
-  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
-    const int start = row_offsets[row], stop = row_offsets[row + 1];
-    for (int i = start + lane; i + 1 < stop; i += 32)
-      ascending &= column_indices[i] <= column_indices[i + 1];
-  }
-  if (!ascending) spmm_sorted = 0;
-}
 
 __global__ void __launch_bounds__(kBulkWarps * 32, 1)
 csr_spmm_bulk_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
@@ -329,11 +318,12 @@ csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__
                       const float *__restrict__ values, const float *__restrict__ dense,
                       float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
                       int64_t output_pitch, int column_lo, int column_hi, int phase) {
-  const bool accumulate = phase > 0;
-  if (!spmm_sorted) {  // some row is not ascending: launch 0 covers every column
-    if (phase > 0) return;
-    column_lo = INT32_MIN;
+  bool accumulate = phase > 0;
+  if (phase > 0 && !spmm_sorted) {  // launch 0 met a row that does not ascend
+    if (phase > 1) return;
+    column_lo = INT32_MIN;          // launch 1 redoes the whole product in storage order
     column_hi = INT32_MAX;
+    accumulate = false;
   }
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kBlockWarps + (threadIdx.x >> 5);
@@ -345,7 +335,8 @@ csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__
   float *destination = output + row * output_pitch + feature;
   if (accumulate && active) acc = __ldcs(reinterpret_cast<const float4 *>(destination));
   const float *source = dense + feature;
-  bool touched = !accumulate;  // launch 0 always writes (rows without a term in the block become 0)
+  bool touched = !accumulate;  // a launch that starts from zero always writes
+  int previous = INT32_MIN;    // last column of the batch before (ascending check of launch 0)
   for (int base = start; base < stop; base += 32) {
     int column = 0;
     float value = 0.0f;
@@ -354,6 +345,12 @@ csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__
       column = __ldcs(column_indices + base + lane);
       value = __ldcs(values + base + lane);
       mine = column >= column_lo && column < column_hi;
+    }
+    if (phase == 0) {
+      const int before = __shfl_up_sync(0xffffffffu, column, 1);
+      const bool descends = base + lane < stop && column < (lane == 0 ? previous : before);
+      if (__any_sync(0xffffffffu, descends) && lane == 0) spmm_sorted = 0;
+      previous = __shfl_sync(0xffffffffu, column, 31);
     }
     unsigned mask = __ballot_sync(0xffffffffu, mine);
     touched |= mask != 0;
@@ -455,11 +452,7 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
     const int64_t resident = sm_count();
     const dim3 grid((unsigned)(wanted < resident ? wanted : resident), (unsigned)((x_d1 + 127) / 128));
     const int phases = column_phases(x_d0, x_d1);
-    if (phases > 1) {
-      spmm_assume_sorted_kernel<<<1, 1, 0, s>>>();
-      spmm_check_sorted_kernel<<<sm_count() * 4, 256, 0, s>>>((const int32_t *)row_offsets,
-                                                             (const int32_t *)column_indices, rows);
-    }
+    if (phases > 1) spmm_assume_sorted_kernel<<<1, 1, 0, s>>>();
     const int64_t block = (x_d0 + phases - 1) / phases;
     const dim3 block_grid((unsigned)((rows + kBlockWarps - 1) / kBlockWarps), grid.y);
     for (int phase = 0; phase < phases; ++phase) {
