@@ -66,11 +66,24 @@ class ClockSampler:
 
     def __init__(self, device_index: int):
         self.device_index, self.samples, self.process = device_index, [], None
+        self.windows = []          # (begin, end) wall-clock intervals with the GPU under the timed load
+
+    def window(self):
+        sampler = self
+
+        class Window:
+            def __enter__(self):
+                self.begin = time.time()
+
+            def __exit__(self, *_):
+                sampler.windows.append((self.begin, time.time()))
+
+        return Window()
 
     def __enter__(self):
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -82,7 +95,7 @@ class ClockSampler:
         for line in self.process.stdout:
             fields = [f.strip() for f in line.split(",")]
             if len(fields) >= 9:
-                self.samples.append(fields)
+                self.samples.append((time.time(), fields))
 
     def __exit__(self, *_):
         if self.process:
@@ -92,9 +105,13 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.process.kill()
 
-    def summary(self) -> dict:
+    def summary(self, windows=None) -> dict:
         clocks, reasons, maximum = [], set(), None
-        for fields in self.samples:
+        windows = self.windows if windows is None else windows
+        for stamp, fields in list(self.samples):
+            # nvidia-smi reports the state of the last ~50 ms; keep samples taken inside a load window
+            if not any(begin + 0.05 <= stamp <= end + 0.05 for begin, end in windows):
+                continue
             try:
                 clocks.append(float(fields[1]))
                 maximum = float(fields[2])
@@ -106,7 +123,8 @@ class ClockSampler:
                     reasons.add(name)
         busy = [c for c in clocks if maximum is None or c > 0]
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": maximum,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+                "reasons": sorted(reasons), "samples": len(clocks),
+                "window": "samples taken while the timed graph replays ran (0.25 s of the same load, then the timed pass)"}
 
 
 # --------------------------------------------------------------------------- operators
@@ -337,6 +355,10 @@ def timed(function, steps: int, warmup: int, distributed: bool, device) -> float
     return max_over_ranks(start.elapsed_time(stop), distributed, device) / steps
 
 
+LOAD_SECONDS = 0.25
+CLOCKS = None  # the ClockSampler of this run
+
+
 def timed_graph(function, steps: int, warmup: int, distributed: bool, device) -> float:
     """Like `timed`, with the K launches captured once in a CUDA graph and replayed, so the
     device time of short kernels is not hidden behind Python's launch cost (the reference's
@@ -351,10 +373,22 @@ def timed_graph(function, steps: int, warmup: int, distributed: bool, device) ->
     graph.replay()
     barrier(distributed)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    window = CLOCKS.window() if CLOCKS is not None else None
+    if window:
+        window.__enter__()
+    # The same load runs for LOAD_SECONDS before the timed pass so that the clock samples
+    # (one per 50 ms) describe the state the timed pass sees: a kernel inside a long step.
+    deadline = time.time() + LOAD_SECONDS
+    while time.time() < deadline:
+        graph.replay()
+        torch.cuda.synchronize()
+    barrier(distributed)
     start.record()
     graph.replay()
     stop.record()
     barrier(distributed)
+    if window:
+        window.__exit__()
     return max_over_ranks(start.elapsed_time(stop), distributed, device) / steps
 
 
@@ -390,23 +424,28 @@ def measure(case, steps: int, warmup: int, distributed: bool, world: int, peak_t
             with_cpu: bool) -> dict:
     workload = case.workload
     scale = 1e6 if workload.unit == "GB/s" else 1e9      # bytes/ms -> GB/s, flop/ms -> TFLOP/s
+    first_window = len(CLOCKS.windows) if CLOCKS is not None else 0
     resident_ms = timed_graph(case.launch, steps, warmup, distributed, case.device)
+    time.sleep(0.06)  # let the sampler deliver the sample that covers the end of the window
+    own_clocks = CLOCKS.summary(CLOCKS.windows[first_window:]) if CLOCKS is not None else None
     e2e_ms = timed(case.e2e, max(2, steps // 4), 1, distributed, case.device)
     per_gpu = workload.work / resident_ms / scale
     if workload.bound == "hbm":
         peak, peak_name = peak_table["hbm_gbs"], f"{peak_kind} STREAM-style copy"
-    else:
-        peak, peak_name = peak_table["bf16_tflops"], f"{peak_kind} cuBLAS bf16 burst"
+        burst = peak
+    else:  # timed after 0.25 s of the same load: the sustained cuBLAS figure is the like-for-like peak
+        peak, peak_name = peak_table["bf16_tflops_sustained"], f"{peak_kind} cuBLAS bf16 sustained"
+        burst = peak_table["bf16_tflops"]
     result = {
         "op": case.name, "workload": workload.description, "unit": workload.unit,
         "value": per_gpu * world, "ms_per_step": resident_ms,
         "e2e": {"value": workload.work / e2e_ms / scale * world, "unit": workload.unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": case.h2d, "d2h_bytes_per_step": case.d2h},
         "roofline": {"bound": workload.bound, "achieved": per_gpu, "peak": peak, "unit": workload.unit,
-                     "frac": per_gpu / peak, "peak_source": peak_name,
+                     "frac": per_gpu / peak, "peak_source": peak_name, "frac_of_burst_peak": per_gpu / burst,
                      "frac_of_nominal": per_gpu / NOMINAL[workload.bound],
                      "traffic": NCU_TRAFFIC_BYTES[case.name], "algorithmic": workload.work},
-        "l2": case.flush,
+        "l2": case.flush, "clocks": own_clocks,
     }
     if with_cpu:
         import oracle
@@ -497,14 +536,17 @@ def main() -> None:
     primary = "layer_norm" if arguments.op == "all" else arguments.op
     names.sort(key=lambda name: name != primary)           # the headline workload runs first
     results, launches = {}, 0
+    global CLOCKS
     with ClockSampler(local_rank) as clocks:
+        CLOCKS = clocks
         for name in names:
             steps = arguments.steps
             try:
                 case = CASES[name](device)
                 results[name] = measure(case, steps, arguments.warmup, distributed, world, peak_table, peak_kind,
                                         with_cpu=(rank == 0 and world == 1))
-                # warm-up + the captured pass + two replays, then the end-to-end warm-up and steps
+                # warm-up, the captured pass, the timed replay (the 0.25 s of load replays before it
+                # are not counted), then the end-to-end warm-up and steps
                 launches += arguments.warmup + 3 * steps + 1 + max(2, steps // 4)
                 del case
             except Exception as error:  # one failing operator must not hide the others
@@ -528,7 +570,8 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": head["workload"], "l2": head["l2"],
                    "parallelism": f"{world} independent shard(s), no data-path collective"},
-        "roofline": head["roofline"], "e2e": head["e2e"], "gpu_launches": launches, "clocks": clock_summary,
+        "roofline": head["roofline"], "e2e": head["e2e"], "gpu_launches": launches,
+        "clocks": head.get("clocks") or clock_summary,
         "ops": [results[name] for name in names],
     }
     if "cpu_baseline" in head:
