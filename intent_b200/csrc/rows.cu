@@ -274,6 +274,22 @@ template <typename T> bool plan_row(int64_t columns, RowPlan *plan) {
   return false;
 }
 
+// CTAs of `kernel` that are resident per SM (register, thread and shared-memory limits),
+// so the persistent grid is exactly one wave.  Cached per kernel and shared-memory size.
+template <typename Kernel>
+int resident_ctas(Kernel kernel, int threads, size_t smem) {
+  static thread_local size_t cached_smem = ~size_t(0);
+  static thread_local int cached = 0;
+  if (cached_smem != smem) {
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, smem) != cudaSuccess || blocks < 1)
+      blocks = 1;
+    cached = blocks;
+    cached_smem = smem;
+  }
+  return cached;
+}
+
 int grid_for(int64_t rows, int groups_per_cta, int ctas_per_sm) {
   const int64_t wanted = (rows + groups_per_cta - 1) / groups_per_cta;
   const int64_t resident = (int64_t)sm_count() * ctas_per_sm;
@@ -284,7 +300,8 @@ template <typename T, int WARPS, int ITERS>
 int launch_softmax_rows(const T *x, T *y, int64_t rows, int64_t columns, int64_t xp, int64_t yp,
                         cudaStream_t stream) {
   using Shape = SoftmaxShape<WARPS>;
-  const int grid = grid_for(rows, Shape::kGroups, 2048 / Shape::kCtaThreads);
+  const int grid = grid_for(rows, Shape::kGroups,
+                            resident_ctas(softmax_rows_kernel<T, WARPS, ITERS>, Shape::kCtaThreads, 0));
   softmax_rows_kernel<T, WARPS, ITERS><<<grid, Shape::kCtaThreads, 0, stream>>>(
       x, y, rows, (int)columns, xp, yp);
   B200_CUDA_TRY(cudaGetLastError());
@@ -342,12 +359,7 @@ int launch_layer_norm_rows(const T *x, const T *w, const T *b, T *y, int64_t row
   if (smem > 48 * 1024)
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kMaxStagedParameterBytes));
-  int ctas_per_sm = 2048 / Shape::kCtaThreads;
-  if (smem) {
-    const int by_smem = (int)((200 * 1024) / (smem + 1024));
-    if (by_smem < ctas_per_sm) ctas_per_sm = by_smem < 1 ? 1 : by_smem;
-  }
-  const int grid = grid_for(rows, Shape::kGroups, ctas_per_sm);
+  const int grid = grid_for(rows, Shape::kGroups, resident_ctas(kernel, Shape::kCtaThreads, smem));
   kernel<<<grid, Shape::kCtaThreads, smem, stream>>>(x, w, b, y, rows, (int)columns, xp, yp,
                                                      inverse_features, epsilon, stage);
   B200_CUDA_TRY(cudaGetLastError());
