@@ -80,6 +80,18 @@ int b200_softmax(const void *x, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_
                  int32_t dtype, void *stream);
 
 /*
+ * Softmax backward: gradient = p * (dy - sum(p * dy)) per row, f32.  Replaces
+ * softmax_backward (python/intent/examples/kernels/backward/softmax.py:9-24), the
+ * kernel the reference pairs with stable_softmax for autograd
+ * (examples/softmax_forward_backward.py:11-29).  Unit inner strides; any row
+ * pitch or alignment (the reference instance has 4097 columns).
+ */
+int b200_softmax_backward(const void *probabilities, int64_t p_d0, int64_t p_d1, int64_t p_s0, int64_t p_s1,
+                          const void *upstream, int64_t u_d0, int64_t u_d1, int64_t u_s0, int64_t u_s1,
+                          void *gradient, int64_t g_d0, int64_t g_d1, int64_t g_s0, int64_t g_s1,
+                          int32_t dtype, void *stream);
+
+/*
  * LayerNorm forward.  Replaces layer_norm_f16 / layer_norm_bf16 (centred
  * two-pass variance) and weighted_layer_norm (f32, E[x^2] - mean^2)
  * (python/intent/examples/kernels/normalization/layer_norm.py:9-85).
@@ -184,6 +196,19 @@ int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
                   const void *dense, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
                   void *output, int64_t y_d0, int64_t y_d1, int64_t y_s0, int64_t y_s1,
                   void *stream);
+
+/*
+ * CSR SpMV  y = A . x: csr_spmm with a single feature, same strict storage-order
+ * accumulation (bit-identical to the sequential sum).  Replaces csr_spmv
+ * (python/intent/examples/kernels/sparse/csr_spmv.py:11-29), the reference's
+ * registered sparse program (python/intent/examples/programs/irregular.py:27-33).
+ * Index/value arrays contiguous; x and y may have any stride.
+ */
+int b200_csr_spmv(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
+                  const void *column_indices, int64_t ci_d0, int64_t ci_s0,
+                  const void *values, int64_t va_d0, int64_t va_s0,
+                  const void *vector, int64_t x_d0, int64_t x_s0,
+                  void *output, int64_t y_d0, int64_t y_s0, void *stream);
 
 /*
  * Device-side check of a CSR structure (monotone offsets within [0,nnz],

@@ -18,10 +18,10 @@ import os
 from . import _native, ops
 from .compilation import (COMPILER, CompilationStageError, CompileOptions, GeneratedProgram, JITKernel,
                   device_capabilities, generate, jit, kernels)
-from .runtime import Artifact, B200Call, B200Program, Interface, register_operator
+from .runtime import Artifact, B200Call, B200Program, Interface, PreparedSequence, register_operator
 
 __all__ = ["register", "jit", "generate", "kernels", "COMPILER", "CompileOptions", "GeneratedProgram",
-           "JITKernel", "Artifact", "B200Program", "B200Call", "Interface", "CompilationStageError",
+           "JITKernel", "Artifact", "PreparedSequence", "B200Program", "B200Call", "Interface", "CompilationStageError",
            "device_capabilities", "register_operator", "ops"]
 
 

@@ -38,6 +38,8 @@ SIGNATURES = {
     "b200_gemm_static_scratch": _view(2) + _view(2) + _view(2) + [_I32, _I32, _I32, _P],
     "b200_flash_attention": _view(4) * 4 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_csr_spmm": _view(1) * 3 + _view(2) * 2 + [_P],
+    "b200_csr_spmv": _view(1) * 5 + [_P],
+    "b200_softmax_backward": _view(2) * 3 + [_I32, _P],
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
     "b200_csr_spmm_status": [ctypes.POINTER(_I64), _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],

@@ -133,6 +133,8 @@ class kernels:
     flash_gqa_attention_fwd = KernelDefinition(
         "flash_gqa_attention_fwd", (((("CAUSAL", True),), "flash_gqa_attention_fwd.mlir"),),
         ("HEAD_GROUP", "CAUSAL"), head_group=True)
+    csr_spmv = KernelDefinition("csr_spmv", (((), "csr_spmv.mlir"),))
+    softmax_backward = KernelDefinition("softmax_backward", (((), "softmax_backward.mlir"),))
     csr_spmm = KernelDefinition("csr_spmm", (((), "csr_spmm.mlir"),))
     csr_spmm_262144 = KernelDefinition("csr_spmm", (((), "csr_spmm_262144.mlir"),))
 

@@ -13,7 +13,7 @@
 // Kernel IR arrives as generic-form MLIR text on stdin.  There is no tile
 // compiler behind this step: the module is classified STRUCTURALLY (operation
 // multiset, operator kinds, element types, parameter shapes — never the
-// kernel's name, doc/getting-started/configuration.en.md:7) into one of five
+// kernel's name, doc/getting-started/configuration.en.md:7) into one of the
 // operator families, each of which has a hand-written sm_100a kernel in
 // libintent_b200.so.  Anything else is refused with the provider_pipeline exit
 // code; there is no fallback.  Outputs: the IR echoed back, a small launch
@@ -388,17 +388,36 @@ Plan classify(const std::vector<Parameter> &all, const std::vector<Operation> &o
     return plan;
   }
   if (c.of("for") == 1) {
-    // ---- CSR SpMM: parallel rows, ordered loop over the row's non-zeros -----
+    // ---- CSR SpMM / SpMV: parallel rows, ordered loop over the row's non-zeros ----
     require(c.of("parallel") == 1 && c.of("view_load") == 5 && c.of("view_store") == 1 &&
                 c.of("assume_in_bounds") == 3 && c.of("binary<multiply>") == 1 && c.of("binary<add>") == 2 &&
-                c.of("binary") == 3 && c.of("unary") == 0 && c.of("reduce") == 0 && c.of("cast") == 0,
+                c.of("binary") == 3 && c.of("unary") == 0 && c.of("reduce") == 0 && c.of("cast") <= 1,
             "loop program is not the CSR row accumulation");
-    require(p.size() == 5 && view_is(p[0], 1, 0, "i32") && view_is(p[1], 1, 0, "i32") && view_is(p[2], 1, 0, "f32") &&
-                view_is(p[3], 2, 0, "f32") && view_is(p[4], 2, 1, "f32"),
-            "csr_spmm takes row_offsets i32, column_indices i32, values f32, dense f32, output f32");
-    plan.family = "csr_spmm";
-    plan.entry = "b200_csr_spmm";
+    require(p.size() == 5 && view_is(p[0], 1, 0, "i32") && view_is(p[1], 1, 0, "i32") && view_is(p[2], 1, 0, "f32"),
+            "CSR kernels take row_offsets i32, column_indices i32, values f32 first");
+    if (view_is(p[3], 1, 0, "f32") && view_is(p[4], 1, 1, "f32")) {
+      plan.family = "csr_spmv";
+      plan.entry = "b200_csr_spmv";
+    } else {
+      require(view_is(p[3], 2, 0, "f32") && view_is(p[4], 2, 1, "f32") && c.of("cast") == 0,
+              "the dense operand and the output must both be f32 vectors or both f32 matrices");
+      plan.family = "csr_spmm";
+      plan.entry = "b200_csr_spmm";
+    }
     plan.contiguous = {0, 1, 2};
+    return plan;
+  }
+  if (!heavy && c.of("parallel") == 1 && c.of("reduce") == 1 && c.of("unary") == 0 && c.of("view_load") == 2 &&
+      c.of("view_store") == 1) {
+    // ---- softmax backward: p * (dy - sum(p * dy)) --------------------------------
+    require(c.of("binary<multiply>") == 2 && c.of("binary<subtract>") == 1 && c.of("binary<add>") == 1 &&
+                c.of("binary") == 4 && c.of("cast") == 0,
+            "single-reduction program is not p * (dy - sum(p * dy))");
+    require(p.size() == 3 && view_is(p[0], 2, 0, "f32") && view_is(p[1], 2, 0, "f32") && view_is(p[2], 2, 1, "f32"),
+            "softmax_backward takes probabilities, upstream, gradient as f32 matrices");
+    plan.family = "softmax_backward";
+    plan.entry = "b200_softmax_backward";
+    plan.tail = {{"dtype", 0}};
     return plan;
   }
   require(!heavy && c.of("parallel") == 1 && c.of("reduce") == 2 && c.of("view_store") == 1, "unrecognised structure");

@@ -7,6 +7,8 @@
 // several warps, one named barrier per reduction.  Row groups stride over the
 // rows (persistent grid sized from the SM count) so LayerNorm's gamma/beta are
 // staged in shared memory once per CTA.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -118,6 +120,37 @@ softmax_generic_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
       destination[c] = Element<T>::narrow(sizeof(T) == 4 ? __fmul_rn(e, inverse) : __fdiv_rn(e, sum));
     }
     __syncthreads();
+  }
+}
+
+// --------------------------------------------------------- softmax backward
+// gradient = p * (dy - sum(p * dy)) per row.  The reference instance has 4097 columns, so
+// rows are not 16-byte aligned: both input rows are staged in shared memory with coalesced
+// scalar loads (each element is read from HBM once), reduced, and written back.
+__global__ void __launch_bounds__(256)
+softmax_backward_kernel(const float *__restrict__ probabilities, const float *__restrict__ upstream,
+                        float *__restrict__ gradient, int64_t rows, int columns, int64_t p_pitch,
+                        int64_t u_pitch, int64_t g_pitch, int staged) {
+  extern __shared__ __align__(16) unsigned char dynamic_smem[];
+  float *p_row = reinterpret_cast<float *>(dynamic_smem);
+  float *u_row = p_row + columns;
+  __shared__ float scratch[8];
+  const int warp = threadIdx.x >> 5;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float *p = probabilities + row * p_pitch, *u = upstream + row * u_pitch;
+    float partial = 0.0f;
+    for (int c = threadIdx.x; c < columns; c += 256) {
+      const float pv = __ldcs(p + c), uv = __ldcs(u + c);
+      if (staged) { p_row[c] = pv; u_row[c] = uv; }
+      partial += __fmul_rn(pv, uv);
+    }
+    const float projection = group_reduce<8, false>(partial, scratch, warp, 1);
+    float *g = gradient + row * g_pitch;
+    for (int c = threadIdx.x; c < columns; c += 256) {
+      const float pv = staged ? p_row[c] : p[c], uv = staged ? u_row[c] : u[c];
+      __stcs(g + c, __fmul_rn(pv, __fsub_rn(uv, projection)));
+    }
+    __syncthreads();  // scratch and the staged rows are reused by the next row
   }
 }
 
@@ -457,4 +490,35 @@ extern "C" int b200_layer_norm(const void *x, int64_t x_d0, int64_t x_d1, int64_
   default: return fail(B200_ERR_INVALID_ARGUMENT, "layer_norm: unknown element type %d", dtype);
   }
 #undef B200_LN_CALL
+}
+
+extern "C" int b200_softmax_backward(const void *p, int64_t p_d0, int64_t p_d1, int64_t p_s0, int64_t p_s1,
+                                     const void *dy, int64_t u_d0, int64_t u_d1, int64_t u_s0, int64_t u_s1,
+                                     void *dx, int64_t g_d0, int64_t g_d1, int64_t g_s0, int64_t g_s1,
+                                     int32_t dtype, void *stream) {
+  if (p_d0 < 0 || p_d1 < 0 || u_d0 != p_d0 || u_d1 != p_d1 || g_d0 != p_d0 || g_d1 != p_d1)
+    return fail(B200_ERR_INVALID_ARGUMENT, "softmax_backward: probabilities, upstream and gradient must share one shape");
+  if (p_d0 == 0 || p_d1 == 0) return B200_OK;
+  if (!p || !dy || !dx) return fail(B200_ERR_INVALID_ARGUMENT, "softmax_backward: null buffer");
+  if (dtype != B200_F32) return fail(B200_ERR_INVALID_ARGUMENT, "softmax_backward: element type %d is not f32", dtype);
+  if (p_d1 > 1 && (p_s1 != 1 || u_s1 != 1 || g_s1 != 1))
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "softmax_backward: inner strides must be 1");
+  if (p_d1 > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "softmax_backward: row too long");
+  const size_t row_bytes = 2 * (size_t)p_d1 * sizeof(float);
+  const int staged = row_bytes <= 96 * 1024;
+  const size_t smem = staged ? row_bytes : 0;
+  if (smem > 48 * 1024) {
+    static std::once_flag configured;
+    static cudaError_t attribute_error = cudaSuccess;
+    std::call_once(configured, [] {
+      attribute_error = cudaFuncSetAttribute(softmax_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    });
+    B200_CUDA_TRY(attribute_error);
+  }
+  const int resident = resident_ctas(softmax_backward_kernel, 256, smem);
+  const int64_t wanted = p_d0, limit = (int64_t)sm_count() * resident;
+  softmax_backward_kernel<<<(unsigned)(wanted < limit ? wanted : limit), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      (const float *)p, (const float *)dy, (float *)dx, p_d0, (int)p_d1, p_s0, u_s0, g_s0, staged);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }

@@ -380,6 +380,30 @@ csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__
   if (active && touched) __stcs(reinterpret_cast<float4 *>(destination), acc);
 }
 
+// CSR SpMV  y = A . x  (csr_spmm with a single feature).  One warp per row: the 32
+// products of a batch are formed in parallel (separately rounded), then added to the
+// carry one by one in storage order, so the sum is the sequential left-to-right one.
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+csr_spmv_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
+                const float *__restrict__ values, const float *__restrict__ vector, float *__restrict__ output,
+                int64_t rows, int64_t vector_stride, int64_t output_stride) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
+  float acc = 0.0f;
+  for (int base = start; base < stop; base += 32) {
+    const int count = min(32, stop - base);
+    float product = 0.0f;
+    if (lane < count) {
+      const int column = __ldcs(column_indices + base + lane);
+      product = __fmul_rn(__ldcs(values + base + lane), __ldg(vector + (int64_t)column * vector_stride));
+    }
+    for (int j = 0; j < count; ++j) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, product, j));
+  }
+  if (lane == 0) output[row * output_stride] = acc;
+}
+
 // Number of column blocks: X is cut into slices of at most kBlockBytes so that a slice
 // stays resident in L2 (126 MB, shared with the streamed index, value and Y traffic).
 constexpr int64_t kBlockBytes = 72ll << 20;
@@ -515,5 +539,28 @@ extern "C" int b200_csr_spmm_status(int64_t *row, void *stream) {
     cudaMemcpyToSymbolAsync(spmm_status, zero, sizeof zero, 0, cudaMemcpyHostToDevice, s);
     return fail(B200_ERR_DEVICE_TIMEOUT, "csr_spmm: a staged gather did not arrive (row %d left unwritten)", words[1]);
   }
+  return B200_OK;
+}
+
+extern "C" int b200_csr_spmv(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
+                             const void *column_indices, int64_t ci_d0, int64_t ci_s0,
+                             const void *values, int64_t va_d0, int64_t va_s0,
+                             const void *vector, int64_t x_d0, int64_t x_s0,
+                             void *output, int64_t y_d0, int64_t y_s0, void *stream) {
+  const int64_t rows = ro_d0 - 1;
+  if (ro_d0 < 1 || ci_d0 < 0 || va_d0 != ci_d0 || x_d0 < 0 || y_d0 != rows)
+    return fail(B200_ERR_INVALID_ARGUMENT, "csr_spmv: inconsistent extents");
+  if (rows == 0) return B200_OK;
+  if (!row_offsets || !output || (ci_d0 > 0 && (!column_indices || !values || !vector)))
+    return fail(B200_ERR_INVALID_ARGUMENT, "csr_spmv: null buffer");
+  if ((ro_d0 > 1 && ro_s0 != 1) || (ci_d0 > 1 && (ci_s0 != 1 || va_s0 != 1)))
+    return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: index/value arrays must be contiguous");
+  if (ci_d0 > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: i32 index space exceeded");
+  const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  if (ctas > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: too many rows");
+  csr_spmv_kernel<<<(unsigned)ctas, kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values, (const float *)vector,
+      (float *)output, rows, x_s0, y_s0);
+  B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

@@ -22,7 +22,8 @@ import sys
 import intent
 from intent.examples.kernels.contraction import gemm as gemm_kernels
 from intent.examples.kernels.normalization import layer_norm, softmax
-from intent.examples.kernels.sparse import csr_spmm
+from intent.examples.kernels.backward import softmax as softmax_backward_kernels
+from intent.examples.kernels.sparse import csr_spmm, csr_spmv
 from intent.examples.kernels.streaming import attention
 
 CASES = {
@@ -40,6 +41,8 @@ CASES = {
     "flash_attention_fwd_noncausal": (attention.flash_attention_fwd, {"CAUSAL": False}),
     "flash_gqa_attention_fwd": (attention.flash_gqa_attention_fwd, {"HEAD_GROUP": 4, "CAUSAL": True}),
     "csr_spmm": (csr_spmm.csr_spmm, None),
+    "csr_spmv": (csr_spmv.csr_spmv, None),
+    "softmax_backward": (softmax_backward_kernels.softmax_backward, None),
     # kernels outside the five families: the compile step must refuse them
     "gemm_f32": (gemm_kernels.gemm_f32, None),
 }

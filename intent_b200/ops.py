@@ -112,6 +112,24 @@ def csr_spmm(row_offsets, column_indices, values, dense, out=None):
     return out
 
 
+def csr_spmv(row_offsets, column_indices, values, vector, out=None):
+    device = _require_cuda(row_offsets, column_indices, values, vector)
+    if out is None:
+        out = torch.empty((row_offsets.numel() - 1,), dtype=torch.float32, device=device)
+    _call("b200_csr_spmv", device, *_slots(row_offsets), *_slots(column_indices), *_slots(values),
+          *_slots(vector), *_slots(out), _stream(vector))
+    return out
+
+
+def softmax_backward(probabilities, upstream, out=None):
+    device = _require_cuda(probabilities, upstream)
+    if out is None:
+        out = torch.empty(probabilities.shape, dtype=probabilities.dtype, device=device)
+    _call("b200_softmax_backward", device, *_slots(probabilities), *_slots(upstream), *_slots(out),
+          _CODES[probabilities.dtype], _stream(probabilities))
+    return out
+
+
 def csr_spmm_status(device) -> None:
     """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
     device = torch.device(device)

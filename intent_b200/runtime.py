@@ -560,6 +560,17 @@ class B200Call:
             _native.check(self.program.facts.entry, status)
         self._record("launched")
 
+    def enqueue(self, queue) -> None:
+        """Submit on a caller-owned CUDA stream (a ``torch.cuda.Stream`` or a raw handle)
+        instead of torch's current one (PreparedSequence.enqueue, runtime/sequence.py:66-69)."""
+        handle = queue.cuda_stream if hasattr(queue, "cuda_stream") else int(queue)
+        with torch.cuda.device(self.program.device):
+            status = self.program.function()(*self.native_arguments, handle)
+        if status != _native.OK:
+            self._record("failed")
+            _native.check(self.program.facts.entry, status)
+        self._record("launched")
+
     def result(self):
         if not self.outputs:
             return None
@@ -580,6 +591,43 @@ class B200Call:
 
     def inspect_configurations(self):
         return self.program.inspect_configurations()
+
+
+class PreparedSequence:
+    """An ordered sequence of already-bound calls (runtime/sequence.py:39-104): construction
+    and compile never launch; launch runs the members in order on the current stream."""
+
+    def __init__(self, calls, *, outputs, owners=()):
+        self.calls = tuple(calls)
+        if not self.calls:
+            raise ValueError("a prepared sequence requires at least one invocation")
+        self._outputs = outputs
+        self._owners = tuple(owners)
+
+    def compile(self):
+        for call in self.calls:
+            call.compile()
+
+    def launch(self):
+        for call in self.calls:
+            call.launch()
+
+    def enqueue(self, queue):
+        for call in self.calls:
+            call.enqueue(queue)
+
+    def result(self):
+        return self._outputs
+
+    @property
+    def kernel_count(self):
+        return sum(call.kernel_count if isinstance(call, PreparedSequence) else 1 for call in self.calls)
+
+    @property
+    def observations(self):
+        return tuple(item for call in self.calls
+                     for item in (call.observations if isinstance(call, PreparedSequence)
+                                  else (call.observation,)) if item is not None)
 
 
 @dataclass

@@ -147,6 +147,27 @@ def csr_spmm(row_offsets, column_indices, values, dense, *, rows: tuple[int, int
     return y
 
 
+def csr_spmv(row_offsets, column_indices, values, vector, *, workers=None):
+    _check_cpu(row_offsets, column_indices, values, vector)
+    rows = row_offsets.numel() - 1
+    y = torch.empty((rows,), dtype=torch.float32)
+    library().oracle_csr_spmv(_ptr(row_offsets), _ptr(column_indices), _ptr(values), _ptr(vector), _ptr(y),
+                              _i64(rows), _i64(vector.stride(0)), _i64(1), _i64(workers or default_workers()))
+    return y
+
+
+def softmax_backward(probabilities, upstream, *, workers=None):
+    _check_cpu(probabilities, upstream)
+    if probabilities.stride(1) != 1 or upstream.stride(1) != 1:
+        raise ValueError("the oracle takes unit inner strides here")
+    g = torch.empty(probabilities.shape, dtype=torch.float32)
+    m, n = probabilities.shape
+    library().oracle_softmax_backward(_ptr(probabilities), _ptr(upstream), _ptr(g), _i64(m), _i64(n),
+                                      _i64(probabilities.stride(0)), _i64(upstream.stride(0)), _i64(g.stride(0)),
+                                      _i64(workers or default_workers()))
+    return g
+
+
 def now_ms() -> float:
     return library().oracle_now_ms()
 

@@ -17,6 +17,8 @@
  *                python/intent/examples/kernels/streaming/attention.py:52-114,
  *                  :150-236, :417-425, :428-553
  *                python/intent/examples/kernels/sparse/csr_spmm.py:12-33
+ *                python/intent/examples/kernels/sparse/csr_spmv.py:11-29
+ *                python/intent/examples/kernels/backward/softmax.py:9-24
  *   numerics     doc/dsl/types-numerics-and-effects.en.md:69-177
  *   C spellings  lib/Serialization/Scalar.cpp:271-302   (fmax signed-zero rule,
  *                  expf, 1.0f/sqrtf)
@@ -547,6 +549,52 @@ int oracle_csr_spmm(const int32_t *row_offsets, const int32_t *column_indices, c
   struct spmm_args s = {row_offsets + row_begin, column_indices, values, dense,
                         output + row_begin * os0, features, ds0, ds1, os0, os1};
   dispatch_team(spmm_rows, &s, rows, workers);
+  return ORACLE_OK;
+}
+
+/* csr_spmv  csr_spmv.py:11-29: the same ordered loop with a scalar carry. */
+struct spmv_args {
+  const int32_t *row_offsets, *column_indices; const float *values, *vector; float *output;
+  int64_t xs0, ys0;
+};
+static void spmv_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct spmv_args *s = opaque;
+  for (int64_t r = begin; r < end; ++r) {
+    float acc = 0.0f;
+    for (int32_t nz = s->row_offsets[r]; nz < s->row_offsets[r + 1]; ++nz)
+      acc = acc + s->values[nz] * s->vector[(int64_t)s->column_indices[nz] * s->xs0];
+    s->output[r * s->ys0] = acc;
+  }
+}
+int oracle_csr_spmv(const int32_t *row_offsets, const int32_t *column_indices, const float *values,
+                    const float *vector, float *output, int64_t rows, int64_t xs0, int64_t ys0, int64_t workers) {
+  struct spmv_args s = {row_offsets, column_indices, values, vector, output, xs0, ys0};
+  dispatch_team(spmv_rows, &s, rows, workers);
+  return ORACLE_OK;
+}
+
+/* softmax_backward  kernels/backward/softmax.py:9-24:
+   gradient = p * (dy - reduce.sum(p * dy)); separate multiply, then the lane reduction. */
+struct softmax_backward_args {
+  const float *p, *u; float *g;
+  int64_t n, ps0, us0, gs0;
+};
+static void softmax_backward_rows(void *opaque, int64_t begin, int64_t end) {
+  const struct softmax_backward_args *a = opaque;
+  for (int64_t r = begin; r < end; ++r) {
+    const float *p = a->p + r * a->ps0, *u = a->u + r * a->us0;
+    float lane[LANES];
+    for (int i = 0; i < LANES; ++i) lane[i] = 0.0f;
+    for (int64_t c = 0; c < a->n; ++c) lane[c % LANES] = lane[c % LANES] + p[c] * u[c];
+    const float projection = lanes_sum(lane);
+    float *g = a->g + r * a->gs0;
+    for (int64_t c = 0; c < a->n; ++c) g[c] = p[c] * (u[c] - projection);
+  }
+}
+int oracle_softmax_backward(const float *p, const float *u, float *g, int64_t m, int64_t n, int64_t ps0,
+                            int64_t us0, int64_t gs0, int64_t workers) {
+  struct softmax_backward_args a = {p, u, g, n, ps0, us0, gs0};
+  dispatch_team(softmax_backward_rows, &a, m, workers);
   return ORACLE_OK;
 }
 

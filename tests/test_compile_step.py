@@ -25,6 +25,8 @@ EXPECTED = {
     "flash_attention_fwd_noncausal": ("flash_attention", {"dtype": 1, "head_group": 1, "causal": 0}),
     "flash_gqa_attention_fwd": ("flash_attention", {"dtype": 1, "head_group": 4, "causal": 1}),
     "csr_spmm": ("csr_spmm", {}),
+    "csr_spmv": ("csr_spmv", {}),
+    "softmax_backward": ("softmax_backward", {"dtype": 0}),
     "csr_spmm_262144": ("csr_spmm", {}),
 }
 

@@ -94,3 +94,50 @@ def test_as_torch_op_eager_and_compiled():
         return op(t) * 2
 
     assert relative_error(twice(x.to(DEV)), oracle.softmax(x) * 2) <= 1e-5
+
+
+def test_backward_pair_registers_with_autograd():
+    """The reference's own recipe (examples/softmax_forward_backward.py:11-29): forward and
+    backward artifacts become torch operators and the backward is registered for autograd."""
+    forward = b200.jit(b200.kernels.stable_softmax)
+    backward = b200.jit(b200.kernels.softmax_backward)
+    x = torch.randn(4096, 4097, device=DEV)
+    forward.prepare(x)
+    backward.prepare(x, x)
+    forward_op = forward.as_torch_op("b200_test::softmax_fwd")
+    backward_op = backward.as_torch_op("b200_test::softmax_bwd")
+
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(output)
+
+    def backward_rule(ctx, upstream):
+        (probabilities,) = ctx.saved_tensors
+        return backward_op(probabilities, upstream.contiguous())
+
+    forward_op.register_autograd(backward_rule, setup_context=setup_context)
+    leaf = x[:64].clone().requires_grad_(True)
+    reference = leaf.detach().double().requires_grad_(True)
+    weights = torch.randn(64, 4097, device=DEV)
+    # the static kernel shape is 4096 x 4097, so run the full matrix and compare a slice
+    full = x.clone().requires_grad_(True)
+    (forward_op(full) * torch.nn.functional.pad(weights, (0, 0, 0, 4032))).sum().backward()
+    (torch.softmax(reference, 1) * weights.double()).sum().backward()
+    assert relative_error(full.grad[:64], reference.grad) <= 1e-4
+
+
+def test_prepared_sequence_and_explicit_stream():
+    (x,) = workloads.softmax_inputs(4096, 4097, seed=8)
+    xd = x.to(DEV)
+    forward = b200.jit(b200.kernels.stable_softmax).prepare(xd)
+    upstream = torch.randn(4096, 4097, device=DEV)
+    backward = b200.jit(b200.kernels.softmax_backward).prepare(forward.result(), upstream)
+    sequence = b200.PreparedSequence([forward, backward], outputs=backward.result())
+    sequence.compile()
+    assert sequence.kernel_count == 2 and not sequence.observations[0].stage == "launched"
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    sequence.enqueue(side)                                   # caller-owned queue
+    side.synchronize()
+    expected = oracle.softmax_backward(oracle.softmax(x[:32]), upstream[:32].cpu())
+    assert relative_error(sequence.result()[:32], expected) <= 1e-4
+    assert [o.stage for o in sequence.observations] == ["launched", "launched"]

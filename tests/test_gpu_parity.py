@@ -205,6 +205,33 @@ def test_csr_spmm_ragged_rows_and_validation():
         ops.csr_validate(bad_offsets.to(DEV), ci.to(DEV), 64)
 
 
+# ------------------------------------------------- spmv and softmax backward
+@pytest.mark.parametrize("rows,columns,per_row", [(32768, 32768, 32), (1000, 77, 40), (5, 3, 2), (4096, 100000, 7)])
+def test_csr_spmv_bit_exact(rows, columns, per_row):
+    ro, ci, va, x = workloads.csr_inputs(rows, columns, per_row, 1, seed=rows)
+    vector = x[:, 0].contiguous()
+    y = ops.csr_spmv(*cuda(ro, ci, va, vector))
+    assert torch.equal(y.cpu(), oracle.csr_spmv(ro, ci, va, vector))
+    wide = torch.zeros(columns, 3)
+    wide[:, 1] = vector                                                # strided x
+    assert torch.equal(ops.csr_spmv(*cuda(ro, ci, va), wide.to(DEV)[:, 1]).cpu(), y.cpu())
+
+
+@pytest.mark.parametrize("m,n", [(64, 4097), (7, 5), (130, 1024), (3, 30000)])
+def test_softmax_backward(m, n):
+    g = torch.Generator().manual_seed(m + n)
+    probabilities = torch.softmax(torch.randn(m, n, generator=g), dim=1)
+    upstream = torch.randn(m, n, generator=g)
+    gradient = ops.softmax_backward(*cuda(probabilities, upstream))
+    assert relative_error(gradient, oracle.softmax_backward(probabilities, upstream)) <= 1e-5
+    # it is the vector-Jacobian product of the forward kernel
+    x = torch.randn(m, n, generator=g, dtype=torch.float64, requires_grad=True)
+    y = torch.softmax(x, dim=1)
+    (expected,) = torch.autograd.grad(y, x, upstream.double())
+    ours = ops.softmax_backward(ops.softmax(x.detach().float().to(DEV)), upstream.to(DEV))
+    assert relative_error(ours, expected) <= 1e-4
+
+
 COLUMN_BLOCK_SCRIPT = """
 import sys, torch
 sys.path.insert(0, %r)

@@ -97,6 +97,18 @@ def test_csr_spmm_is_the_sequential_sum_and_validates():
         oracle.csr_validate(ro, broken, 300)
 
 
+def test_csr_spmv_and_softmax_backward():
+    ro, ci, va, x = workloads.csr_inputs(300, 500, 40, 1, seed=17)
+    vector = x[:, 0].contiguous()
+    y = oracle.csr_spmv(ro, ci, va, vector)
+    assert torch.equal(y, oracle.csr_spmm(ro, ci, va, x)[:, 0])        # a single-feature SpMM
+    g = torch.Generator().manual_seed(19)
+    probabilities = torch.softmax(torch.randn(33, 4097, generator=g), dim=1)
+    upstream = torch.randn(33, 4097, generator=g)
+    expected = probabilities.double() * (upstream.double() - (probabilities.double() * upstream.double()).sum(1, keepdim=True))
+    assert relative_error(oracle.softmax_backward(probabilities, upstream), expected) <= 1e-5
+
+
 def test_committed_vectors():
     vectors = torch.load(GOLDEN)
     (x,) = workloads.softmax_inputs(4, 16, seed=100)
