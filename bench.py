@@ -48,7 +48,7 @@ NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/ (null where no capture of that kernel exists yet).
 NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1059080448,
-                     "spmm": 975351808}
+                     "spmm": 975351808, "softmax_backward": None, "spmv": None}
 
 
 def peaks() -> tuple[dict, str]:
@@ -322,8 +322,75 @@ class SpmmCase(Case):
         return lambda: oracle.csr_spmm(*self.host, workers=workers), 1.0, "full workload (262144 rows)"
 
 
+class SoftmaxBackwardCase(Case):
+    name = "softmax_backward"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.softmax_backward_workload()
+        self.host = self.workloads.softmax_backward_inputs()
+        self.p, self.u = (t.to(device) for t in self.host)
+        self.g = torch.empty_like(self.p)
+        self.flush = "inputs larger than L2 (201 MB per launch vs 126 MB)"
+        self.kernel = b200.jit(b200.kernels.softmax_backward)
+        self.host_in = [pinned(t) for t in self.host]
+        self.dev_in = [torch.empty_like(self.p) for _ in range(2)]
+        self.host_out = torch.empty_like(self.host[0]).pin_memory()
+        self.call = self.kernel.prepare(*self.dev_in)
+        self.h2d, self.d2h = 2 * self.p.numel() * 4, self.p.numel() * 4
+
+    def launch(self, step):
+        self.ops.softmax_backward(self.p, self.u, out=self.g)
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        return lambda: oracle.softmax_backward(*self.host, workers=workers), 1.0, "full workload (4096 rows)"
+
+
+class SpmvCase(Case):
+    name = "spmv"
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.spmv_workload()
+        ro, ci, va, x = self.workloads.csr_inputs(32768, 32768, 32, 1)
+        self.host = (ro, ci, va, x[:, 0].contiguous())
+        # 8.6 MB per launch fits L2: rotate over 20 copies of the matrix (172 MB) so DRAM is measured
+        self.sets = [[t.to(device) + 0 for t in self.host] + [torch.empty(32768, device=device)] for _ in range(20)]
+        self.flush = "rotating 20 copies of the operands (172 MB > L2)"
+        self.kernel = b200.jit(b200.kernels.csr_spmv)
+        self.host_in = [pinned(t) for t in self.host]
+        self.dev_in = [torch.empty_like(t) for t in self.sets[0][:4]]
+        self.host_out = torch.empty(32768).pin_memory()
+        self.call = self.kernel.prepare(*self.dev_in)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.d2h = 32768 * 4
+
+    def launch(self, step):
+        ro, ci, va, x, y = self.sets[step % len(self.sets)]
+        self.ops.csr_spmv(ro, ci, va, x, out=y)
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.call.launch()
+        self.host_out.copy_(self.call.result(), non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        return lambda: oracle.csr_spmv(*self.host, workers=workers), 1.0, "full workload (32768 rows)"
+
+
 CASES = {"softmax": SoftmaxCase, "layer_norm": LayerNormCase, "gemm": GemmCase, "attention": AttentionCase,
-         "spmm": SpmmCase}
+         "spmm": SpmmCase, "softmax_backward": SoftmaxBackwardCase, "spmv": SpmvCase}
 
 
 # --------------------------------------------------------------------------- timing
@@ -566,7 +633,8 @@ def main() -> None:
         "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": arguments.steps,
         "warmup": arguments.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
-        "dtype": {"softmax": "f32", "layer_norm": "f16", "gemm": "f16", "attention": "bf16", "spmm": "f32"}[primary],
+        "dtype": {"softmax": "f32", "layer_norm": "f16", "gemm": "f16", "attention": "bf16", "spmm": "f32",
+                  "softmax_backward": "f32", "spmv": "f32"}[primary],
         "data": "synthetic",
         "config": {"workload": head["workload"], "l2": head["l2"],
                    "parallelism": f"{world} independent shard(s), no data-path collective"},

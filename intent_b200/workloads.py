@@ -118,3 +118,22 @@ def spmm_workload(rows=262144, columns=262144, per_row=32, features=128) -> Work
     compulsory = (rows + 1) * 4 + nnz * 8 + columns * features * 4 + rows * features * 4
     return Workload("spmm", "GB/s", "hbm", float(compulsory),
                     f"CSR SpMM fp32 {rows}x{columns}, {per_row} nnz/row, X {columns}x{features}")
+
+
+def softmax_backward_inputs(m: int = 4096, n: int = 4097, seed: int = 0):
+    """Probabilities of a seeded N(0,1) score matrix and an N(0,1) upstream gradient; the
+    shape is the reference kernel's static one (kernels/backward/softmax.py:5-6)."""
+    rng = np.random.default_rng(seed)
+    scores = _f32(rng.standard_normal((m, n), dtype=np.float32))
+    upstream = _f32(rng.standard_normal((m, n), dtype=np.float32))
+    return torch.softmax(scores, dim=1), upstream
+
+
+def softmax_backward_workload(m=4096, n=4097) -> Workload:
+    return Workload("softmax_backward", "GB/s", "hbm", 3.0 * m * n * 4, f"softmax backward fp32 {m}x{n}")
+
+
+def spmv_workload(rows=32768, columns=32768, per_row=32) -> Workload:
+    nnz = rows * per_row
+    return Workload("spmv", "GB/s", "hbm", float((rows + 1) * 4 + nnz * 8 + columns * 4 + rows * 4),
+                    f"CSR SpMV fp32 {rows}x{columns}, {per_row} nnz/row")
