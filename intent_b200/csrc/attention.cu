@@ -9,24 +9,30 @@
 // so that while the softmax warps of one tile work on their scores the tensor
 // pipe runs the other tile's two MMAs: each softmax has two MMA slots of cover.
 //
-//   warp 0      TMA producer: Q_A, Q_B once, then K_j, V_j, K_j+1, ... through a
-//               ring of five 32 KB slots (128 rows x 128 B in two 64-column
-//               halves, 128-byte swizzle)
-//   warp 1      MMA issuer:  S = Q . K_j^T   (A, B from shared memory, K-major)
-//                            O += P . V_j    (A = P from TMEM, B = V MN-major)
-//   warps 2..5  softmax of tile A, warps 6..9 softmax of tile B: thread r owns
-//               query row r of its tile.  tcgen05.ld the 128 scores, row maximum,
-//               p = ex2.approx.ftz(s*scale*log2e - m), f32 row sum, P rounded to
-//               the operand type and written back over the score columns
-//               (tcgen05.st).  The running maximum is only replaced, and O and the
-//               sum rescaled, when it grows by more than 2^8: the accumulator stays
-//               exact in the usual online-softmax sense while rescales stay rare.
-//               Last: O * div.approx.ftz(1, sum) -> global.
+//   warp 0       TMA producer: Q_A, Q_B once, then K_j, V_j, K_j+1, ... through a
+//                ring of four 32 KB slots (128 rows x 128 B in two 64-column
+//                halves, 128-byte swizzle)
+//   warp 1       MMA issuer:  S = Q . K_j^T   (A, B from shared memory, K-major)
+//                             O += P . V_j    (A = P from TMEM, B = V MN-major),
+//                issued as two halves of 64 keys, each as soon as its P is ready
+//   warps 2..9   softmax of tile A, warps 10..17 softmax of tile B.  Two threads
+//                share a query row: thread (row, h) owns the score columns
+//                [32h, 32h+32) and [64+32h, 64+32h+32).  Pass 1 reads them from
+//                TMEM (tcgen05.ld) for the row maximum, which the two threads
+//                exchange through shared memory; pass 2 reads them again, 32 at a
+//                time, p = ex2.approx.ftz(s*scale*log2e - m), f32 partial row sum,
+//                P rounded to the operand type and written over the first 16 of
+//                the 32 score columns it came from (tcgen05.st), then the half's
+//                barrier is signalled.  The running maximum is only replaced, and
+//                O and the sums rescaled, when it grows by more than 2^8: the
+//                accumulator stays exact in the usual online-softmax sense while
+//                rescales stay rare.  Last: the two partial sums are added and
+//                each thread writes its half of O * div.approx.ftz(1, sum).
 //
-// TMEM (512 columns): S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512);
-// P aliases the first 64 columns of its S.  Causal tiles that lie entirely above
-// the diagonal are never visited (tile A stops one key tile before tile B); the
-// diagonal tile and the ragged last key tile are masked element-wise.
+// TMEM (512 columns): S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512).
+// Causal tiles that lie entirely above the diagonal are never visited (tile A
+// stops one key tile before tile B); the diagonal tile and the ragged last key
+// tile are masked element-wise.
 // Work per launch: 4*B*H*D*S*(S+1)/2 flop (causal), 4*B*H*S*D*2 compulsory bytes.
 #include <mutex>
 #include <type_traits>
@@ -39,9 +45,9 @@ namespace {
 constexpr int kBlockM = 128;                     // query rows per tile (two tiles per CTA)
 constexpr int kBlockN = 128;
 constexpr int kMaxHeadDim = 128;                 // head dimension is a template parameter: 64 or 128
-constexpr int kThreads = 320;
+constexpr int kThreads = 576;                    // producer warp, MMA warp, 2 tiles x 2 column halves x 4 warps
 constexpr int kTmemColumns = 512;
-constexpr int kRingSlots = 5;
+constexpr int kRingSlots = 4;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // shared-memory slot of one Q / K / V tile (half used at head dim 64)
 constexpr uint32_t kHalfBytes = kTileBytes / 2;  // 64-column half
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
@@ -49,9 +55,12 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 units
 struct __align__(8) Barriers {
   uint64_t q_full;
   uint64_t slot_full[kRingSlots], slot_empty[kRingSlots];
-  uint64_t s_full[2], p_ready[2], o_full[2];
+  uint64_t s_full[2], p_ready[2][2], o_full[2];   // p_ready: [tile][64-key half of the step]
   uint32_t tmem_base;
   int abort_flag;
+  // the two threads that share a query row (one per column half) exchange their maxima and sums here
+  float exchange[2][2][2][kBlockM];   // maxima: [tile][step parity][column half][row]
+  float sums[2][2][kBlockM];          // [tile][column half][row]
 };
 
 constexpr size_t kSmemBytes = 1024 + (2 + kRingSlots) * kTileBytes + sizeof(Barriers);
@@ -66,6 +75,9 @@ __device__ __forceinline__ float ex2_approx_ftz(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ float div_approx_ftz(float a, float b) {
   float y;
@@ -127,7 +139,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     for (int x = 0; x < 2; ++x) {
       tc::mbar_init(&bars->s_full[x], 1);
-      tc::mbar_init(&bars->p_ready[x], 4);
+      tc::mbar_init(&bars->p_ready[x][0], 8);
+      tc::mbar_init(&bars->p_ready[x][1], 8);
       tc::mbar_init(&bars->o_full[x], 1);
     }
     bars->abort_flag = 0;
@@ -201,15 +214,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tc::mma_commit(&bars->s_full[x]);
       };
       // O_x += P_x(j) . V_j; P is read from the first 64 (packed) score columns of tile x
+      // O_x += P_x(j) . V_j in two halves of 64 keys, each as soon as its part of P is in TMEM.
+      // Key block kk (16 keys, 8 packed columns) was written by column half (kk%4)/2 of the softmax
+      // warps into its own score columns: (kk/4)*64 + ((kk%4)/2)*32 + (kk%2)*8.
       auto issue_values = [&](int x, int j) -> bool {
-        if (!tc::mbar_wait(&bars->p_ready[x], j & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) return false;
-        tc::tc_fence_after_sync();
         const uint32_t v_address = ring_address + RingPosition(2 * j + 1).slot * kTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          // A: 16 keys = 8 packed TMEM columns; B: 16 key rows = 2048 bytes further down the V tile
-          tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kMaxHeadDim, tmem_base + x * kBlockN + kk * 8,
-                         tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes), idesc_o, (j | kk) != 0);
+        for (int part = 0; part < 2; ++part) {
+          if (!tc::mbar_wait(&bars->p_ready[x][part], j & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) return false;
+          tc::tc_fence_after_sync();
+#pragma unroll
+          for (int kk = part * 4; kk < part * 4 + 4; ++kk) {
+            const uint32_t p_column = (kk / 4) * 64 + ((kk % 4) / 2) * 32 + (kk % 2) * 8;
+            // B: 16 key rows = 2048 bytes further down the V tile
+            tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kMaxHeadDim, tmem_base + x * kBlockN + p_column,
+                           tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes), idesc_o, (j | kk) != 0);
+          }
         }
         if (j == tiles_of[x] - 1) tc::mma_commit(&bars->o_full[x]);
         return true;
@@ -239,49 +259,53 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else {
     // -------------------------------------------------------------- softmax
-    const int x = (warp - 2) >> 2;                // 0: tile A (warps 2..5), 1: tile B (warps 6..9)
+    const int x = (warp - 2) >> 3;                // 0: tile A (warps 2..9), 1: tile B (warps 10..17)
+    const int half = ((warp - 2) >> 2) & 1;       // which 64 of the 128 score columns this thread owns
     const int quadrant = warp & 3;                // TMEM lanes [32*quadrant, +32) are this warp's
     const int row_in_tile = quadrant * 32 + lane;
+    const int pair_barrier = 1 + x * 4 + quadrant;  // the two warps that own the same 32 rows
     const int tile_q0 = q0 + x * kBlockM;
     const int q_row = tile_q0 + row_in_tile;
     const int my_tiles = tiles_of[x];
+    constexpr int kColumns = kBlockN / 2;         // scores per thread and step
+    constexpr int kOutColumns = kHeadDim / 2;     // output columns per thread
     const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
     const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
     float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
-    float sum = 0.0f;
+    float sum = 0.0f;             // of this thread's columns only; the halves are added at the end
     bool alive = true;
     for (int j = 0; alive && j < my_tiles; ++j) {
       const uint32_t phase = j & 1;
       if (!tc::mbar_wait(&bars->s_full[x], phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
       tc::tc_fence_after_sync();
-      float s[kBlockN];
-#pragma unroll
-      for (int chunk = 0; chunk < kBlockN / 32; ++chunk) {
-        uint32_t raw[32];
-        tc::tmem_load_32x32(tmem_s + lane_base + chunk * 32, raw);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[chunk * 32 + i] = __uint_as_float(raw[i]);
-      }
-      tc::tmem_load_wait();
-      const int k0 = j * kBlockN;
-      const bool masked_tile = (k0 + kBlockN > shape.seq_k) || (shape.causal && k0 + kBlockN - 1 > tile_q0);
-      if (masked_tile) {
-        const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
-#pragma unroll
-        for (int i = 0; i < kBlockN; ++i)
-          if (i >= limit) s[i] = -INFINITY;
-      }
-      // eight independent running maxima keep the dependent chain 16 deep instead of 128
+      // Two passes over this thread's scores (TMEM reads are cheap) keep 32 of them in registers at a
+      // time; P only ever goes over columns this thread has already consumed.
+      const uint32_t my_scores = tmem_s + lane_base + half * 32;   // chunk c: + c * 64
+      const int k0 = j * kBlockN + half * 32;                      // first key of chunk 0; chunk 1: + 64
+      const bool masked_tile = (j * kBlockN + kBlockN > shape.seq_k) || (shape.causal && j * kBlockN + kBlockN - 1 > tile_q0);
+      // columns of chunk c at or beyond limit - c*64 hold no valid key
+      const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
       float partial_max[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) partial_max[u] = s[u];
+      for (int u = 0; u < 8; ++u) partial_max[u] = -INFINITY;
 #pragma unroll
-      for (int i = 8; i < kBlockN; i += 8)
+      for (int chunk = 0; chunk < kColumns / 32; ++chunk) {
+        uint32_t raw[32];
+        tc::tmem_load_32x32(my_scores + chunk * 64, raw);
+        tc::tmem_load_wait();
+        if (masked_tile) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) partial_max[u] = fmaxf(partial_max[u], s[i + u]);
+          for (int i = 0; i < 32; ++i)
+            if (chunk * 64 + i >= limit) raw[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) partial_max[i & 7] = fmaxf(partial_max[i & 7], __uint_as_float(raw[i]));
+      }
       float tile_max = fmaxf(fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])),
                              fmaxf(fmaxf(partial_max[4], partial_max[5]), fmaxf(partial_max[6], partial_max[7])));
-      tile_max *= shape.scale_log2;
+      bars->exchange[x][phase][half][row_in_tile] = tile_max;
+      named_barrier_sync(pair_barrier, 64);
+      tile_max = fmaxf(tile_max, bars->exchange[x][phase][half ^ 1][row_in_tile]) * shape.scale_log2;
       // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
       const bool grow = tile_max > reference + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow)) {
@@ -290,47 +314,60 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (j > 0) {
           // S(j) has completed, hence this tile's P.V(j-1) too: O is quiescent until p_ready is signalled
 #pragma unroll 1
-          for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
+          for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
             uint32_t raw[32];
-            tc::tmem_load_32x32(tmem_o + lane_base + chunk * 32, raw);
+            tc::tmem_load_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
             tc::tmem_load_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * factor);
-            tc::tmem_store_32x32(tmem_o + lane_base + chunk * 32, raw);
+            tc::tmem_store_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
           }
         }
       }
       const float offset = -reference;
       float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int chunk = 0; chunk < kBlockN / 64; ++chunk) {
-        uint32_t packed[32];
+      for (int chunk = 0; chunk < kColumns / 32; ++chunk) {
+        uint32_t raw[32];
+        tc::tmem_load_32x32(my_scores + chunk * 64, raw);
+        tc::tmem_load_wait();
+        if (masked_tile) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i], shape.scale_log2, offset));
-          const float p1 = ex2_approx_ftz(fmaf(s[chunk * 64 + 2 * i + 1], shape.scale_log2, offset));
+          for (int i = 0; i < 32; ++i)
+            if (chunk * 64 + i >= limit) raw[i] = 0xff800000u;
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(raw[2 * i]), shape.scale_log2, offset));
+          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(raw[2 * i + 1]), shape.scale_log2, offset));
           partial_sum[(2 * i) & 3] += p0;
           partial_sum[(2 * i + 1) & 3] += p1;
           packed[i] = pack_pair<T>(p0, p1);
         }
-        tc::tmem_store_32x32(tmem_s + lane_base + chunk * 32, packed);
+        tc::tmem_store_32x16(my_scores + chunk * 64, packed);
+        tc::tmem_store_wait();
+        tc::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&bars->p_ready[x][chunk]);
       }
       sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
-      tc::tmem_store_wait();
-      tc::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&bars->p_ready[x]);
     }
+    // the row sum is the sum of both halves (they share the reference maximum)
+    bars->sums[x][half][row_in_tile] = sum;
+    named_barrier_sync(pair_barrier, 64);
+    sum += bars->sums[x][half ^ 1][row_in_tile];
     if (alive && tc::mbar_wait(&bars->o_full[x], 0, abort_flag, status, tc::kSiteEpilogueTmemFull)) {
       tc::tc_fence_after_sync();
       const float inverse = div_approx_ftz(1.0f, sum);
-      T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s;
+      T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s +
+                       half * kOutColumns;
       const bool vector_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && shape.o_stride_b % 8 == 0 &&
                              shape.o_stride_h % 8 == 0 && shape.o_stride_s % 8 == 0;
 #pragma unroll 1
-      for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
+      for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
         uint32_t raw[32];
-        tc::tmem_load_32x32(tmem_o + lane_base + chunk * 32, raw);
+        tc::tmem_load_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
         tc::tmem_load_wait();
         if (q_row < shape.seq_q) {
           if (vector_ok) {
