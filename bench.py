@@ -46,9 +46,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
-# summarised under profiles/ (null where no capture of that kernel exists yet).
-NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1059080448,
-                     "spmm": 975351808, "softmax_backward": None, "spmv": None}
+# summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1057477120,
+                     "spmm": 975351808, "softmax_backward": 161898752, "spmv": 8655872}
 
 
 def peaks() -> tuple[dict, str]:
