@@ -48,7 +48,7 @@ NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/.
 NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1057477120,
-                     "spmm": 975351808, "softmax_backward": 161898752, "spmv": 8655872}
+                     "spmm": 975351808, "softmax_backward": 161898752, "spmv": 8655872, "layer_norm_backward": None}
 
 
 def peaks() -> tuple[dict, str]:
@@ -132,6 +132,7 @@ class Case:
     """One operator on one device: resident launch, end-to-end launch, CPU sample."""
 
     name = ""
+    launches_per_step = 1      # kernels of ours one step launches
 
     def __init__(self, device):
         from intent_b200 import workloads
@@ -291,6 +292,7 @@ class AttentionCase(Case):
 
 class SpmmCase(Case):
     name = "spmm"
+    launches_per_step = 2      # two column-block launches at this shape
 
     def __init__(self, device):
         super().__init__(device)
@@ -389,8 +391,59 @@ class SpmvCase(Case):
         return lambda: oracle.csr_spmv(*self.host, workers=workers), 1.0, "full workload (32768 rows)"
 
 
+class LayerNormBackwardCase(Case):
+    """Row kernel + partial-sum reduction (two launches per step)."""
+    name = "layer_norm_backward"
+    launches_per_step = 2
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.layer_norm_backward_workload()
+        *tensors, self.inverse = self.workloads.layer_norm_backward_inputs()
+        self.host = tuple(tensors)
+        self.dev = [t.to(device) for t in self.host]
+        self.dx = torch.empty_like(self.dev[0])
+        self.dw = torch.empty(4096, device=device)
+        self.db = torch.empty(4096, device=device)
+        self.flush = "three 33.5 MB matrices per launch; L2 flushed between timed steps is not needed: x, dy are streamed with evict-first loads and 101 MB of distinct lines move per step"
+        self.rows = b200.jit(b200.kernels.layer_norm_backward_rows)
+        self.reduce = b200.jit(b200.kernels.layer_norm_backward_reduce)
+        self.host_in = [pinned(t) for t in self.host]
+        self.dev_in = [torch.empty_like(t) for t in self.dev]
+        self.rows_call = self.rows.prepare(*self.dev_in, self.inverse)
+        self.reduce_call = self.reduce.prepare(self.dev_in[5], self.dev_in[6])
+        self.host_out = [torch.empty_like(self.host[0]).pin_memory(), torch.empty(4096).pin_memory(),
+                         torch.empty(4096).pin_memory()]
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+
+    def launch(self, step):
+        self.ops.layer_norm_backward_rows(*self.dev, self.inverse, out=self.dx)
+        self.ops.layer_norm_backward_reduce(self.dev[5], self.dev[6], dw=self.dw, db=self.db)
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.rows_call.launch()
+        self.reduce_call.launch()
+        dw, db = self.reduce_call.result()
+        for host, dev in zip(self.host_out, (self.rows_call.result(), dw, db)):
+            host.copy_(dev, non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        x, dy, w, mean, rstd, dw_partial, db_partial = self.host
+
+        def run():
+            oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, self.inverse, workers=workers)
+            oracle.layer_norm_backward_reduce(dw_partial, db_partial, workers=workers)
+        return run, 1.0, "full workload (4096 rows, rows + reduce)"
+
+
 CASES = {"softmax": SoftmaxCase, "layer_norm": LayerNormCase, "gemm": GemmCase, "attention": AttentionCase,
-         "spmm": SpmmCase, "softmax_backward": SoftmaxBackwardCase, "spmv": SpmvCase}
+         "spmm": SpmmCase, "softmax_backward": SoftmaxBackwardCase, "spmv": SpmvCase,
+         "layer_norm_backward": LayerNormBackwardCase}
 
 
 # --------------------------------------------------------------------------- timing
@@ -614,7 +667,7 @@ def main() -> None:
                                         with_cpu=(rank == 0 and world == 1))
                 # warm-up, the captured pass, the timed replay (the 0.25 s of load replays before it
                 # are not counted), then the end-to-end warm-up and steps
-                launches += arguments.warmup + 3 * steps + 1 + max(2, steps // 4)
+                launches += case.launches_per_step * (arguments.warmup + 3 * steps + 1 + max(2, steps // 4))
                 del case
             except Exception as error:  # one failing operator must not hide the others
                 if name == primary:
@@ -634,7 +687,7 @@ def main() -> None:
         "warmup": arguments.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
         "dtype": {"softmax": "f32", "layer_norm": "f16", "gemm": "f16", "attention": "bf16", "spmm": "f32",
-                  "softmax_backward": "f32", "spmv": "f32"}[primary],
+                  "softmax_backward": "f32", "spmv": "f32", "layer_norm_backward": "bf16"}[primary],
         "data": "synthetic",
         "config": {"workload": head["workload"], "l2": head["l2"],
                    "parallelism": f"{world} independent shard(s), no data-path collective"},

@@ -92,6 +92,39 @@ int b200_softmax_backward(const void *probabilities, int64_t p_d0, int64_t p_d1,
                           int32_t dtype, void *stream);
 
 /*
+ * LayerNorm backward, row kernel (bf16 operands, f32 arithmetic).  Replaces
+ * layer_norm_backward_rows (python/intent/examples/kernels/backward/layer_norm.py:12-66):
+ * dx = (w*dy - mean(w*dy) - xhat * mean(w*dy*xhat)) * rstd with xhat = (x - mean) * rstd,
+ * and the scatter-reductions dw_partial[row % G] += bf16(dy * xhat),
+ * db_partial[row % G] += dy, G = dw_d0.  The reference promises no order for
+ * colliding updates (doc/dsl/types-numerics-and-effects.en.md:242); this entry
+ * applies the rows of a group in ascending order, each update rounded to bf16,
+ * so results do not vary from run to run.  dw_partial / db_partial are InOut:
+ * their contents are accumulated into.  Unit inner strides; N a multiple of 8
+ * and at most 8192; x, dy, dx, the partial rows and weight 16-byte aligned
+ * (else B200_ERR_UNSUPPORTED_LAYOUT).
+ */
+int b200_layer_norm_backward_rows(const void *x, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
+                                  const void *dy, int64_t dy_d0, int64_t dy_d1, int64_t dy_s0, int64_t dy_s1,
+                                  const void *weight, int64_t w_d0, int64_t w_s0,
+                                  const void *mean, int64_t mean_d0, int64_t mean_s0,
+                                  const void *rstd, int64_t rstd_d0, int64_t rstd_s0,
+                                  void *dx, int64_t dx_d0, int64_t dx_d1, int64_t dx_s0, int64_t dx_s1,
+                                  void *dw_partial, int64_t dw_d0, int64_t dw_d1, int64_t dw_s0, int64_t dw_s1,
+                                  void *db_partial, int64_t db_d0, int64_t db_d1, int64_t db_s0, int64_t db_s1,
+                                  float inverse_features, void *stream);
+
+/*
+ * LayerNorm backward, reduction of the partial sums: dw[n] = sum_g f32(dw_partial[g, n]),
+ * likewise db, groups ascending.  Replaces layer_norm_backward_reduce
+ * (python/intent/examples/kernels/backward/layer_norm.py:69-90).  Unit inner strides.
+ */
+int b200_layer_norm_backward_reduce(const void *dw_partial, int64_t dw_d0, int64_t dw_d1, int64_t dw_s0, int64_t dw_s1,
+                                    const void *db_partial, int64_t db_d0, int64_t db_d1, int64_t db_s0, int64_t db_s1,
+                                    void *dw, int64_t o_d0, int64_t o_s0, void *db, int64_t b_d0, int64_t b_s0,
+                                    void *stream);
+
+/*
  * LayerNorm forward.  Replaces layer_norm_f16 / layer_norm_bf16 (centred
  * two-pass variance) and weighted_layer_norm (f32, E[x^2] - mean^2)
  * (python/intent/examples/kernels/normalization/layer_norm.py:9-85).

@@ -135,6 +135,9 @@ class kernels:
         ("HEAD_GROUP", "CAUSAL"), head_group=True)
     csr_spmv = KernelDefinition("csr_spmv", (((), "csr_spmv.mlir"),))
     softmax_backward = KernelDefinition("softmax_backward", (((), "softmax_backward.mlir"),))
+    layer_norm_backward_rows = KernelDefinition("layer_norm_backward_rows", (((), "layer_norm_backward_rows.mlir"),))
+    layer_norm_backward_reduce = KernelDefinition("layer_norm_backward_reduce",
+                                                  (((), "layer_norm_backward_reduce.mlir"),))
     csr_spmm = KernelDefinition("csr_spmm", (((), "csr_spmm.mlir"),))
     csr_spmm_262144 = KernelDefinition("csr_spmm", (((), "csr_spmm_262144.mlir"),))
 

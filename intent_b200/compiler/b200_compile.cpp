@@ -407,6 +407,32 @@ Plan classify(const std::vector<Parameter> &all, const std::vector<Operation> &o
     plan.contiguous = {0, 1, 2};
     return plan;
   }
+  if (!heavy && c.of("scatter_reduce") == 2) {
+    // ---- LayerNorm backward, per row: dx and the bf16 partial sums of dw, db ------
+    require(c.of("parallel") == 1 && c.of("reduce") == 2 && c.of("view_load") == 5 && c.of("view_store") == 1 &&
+                c.of("unary") == 0 && c.of("cast") == 6 && c.of("binary") == 16 && c.of("binary<multiply>") == 8 &&
+                c.of("binary<subtract>") == 3 && c.of("binary<add>") == 4 && c.of("binary<remainder>") == 1,
+            "scatter-reduction program is not the LayerNorm backward row kernel");
+    require(p.size() == 9 && view_is(p[0], 2, 0, "bf16") && view_is(p[1], 2, 0, "bf16") && view_is(p[2], 1, 0, "bf16") &&
+                view_is(p[3], 1, 0, "f32") && view_is(p[4], 1, 0, "f32") && view_is(p[5], 2, 1, "bf16") &&
+                view_is(p[6], 2, 2, "bf16") && view_is(p[7], 2, 2, "bf16") && p[8].kind == Parameter::kScalar &&
+                p[8].dtype == "f32",
+            "layer_norm_backward_rows takes x, dy, weight, mean, rstd, dx, dw_partial, db_partial, inverse_features");
+    plan.family = "layer_norm_backward_rows";
+    plan.entry = "b200_layer_norm_backward_rows";
+    return plan;
+  }
+  if (!heavy && c.of("parallel") == 0 && c.of("reduce") == 2 && c.of("view_load") == 2 && c.of("view_store") == 2) {
+    // ---- LayerNorm backward, reduction of the partial sums over the group axis ------
+    require(c.of("cast") == 2 && c.of("unary") == 0 && c.of("binary") == 2 && c.of("binary<add>") == 2,
+            "two-output reduction is not the LayerNorm backward partial-sum reduction");
+    require(p.size() == 4 && view_is(p[0], 2, 0, "bf16") && view_is(p[1], 2, 0, "bf16") && view_is(p[2], 1, 1, "f32") &&
+                view_is(p[3], 1, 1, "f32"),
+            "layer_norm_backward_reduce takes dw_partial, db_partial (bf16) and dw, db (f32)");
+    plan.family = "layer_norm_backward_reduce";
+    plan.entry = "b200_layer_norm_backward_reduce";
+    return plan;
+  }
   if (!heavy && c.of("parallel") == 1 && c.of("reduce") == 1 && c.of("unary") == 0 && c.of("view_load") == 2 &&
       c.of("view_store") == 1) {
     // ---- softmax backward: p * (dy - sum(p * dy)) --------------------------------

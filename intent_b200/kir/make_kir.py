@@ -22,6 +22,7 @@ import sys
 import intent
 from intent.examples.kernels.contraction import gemm as gemm_kernels
 from intent.examples.kernels.normalization import layer_norm, softmax
+from intent.examples.kernels.backward import layer_norm as layer_norm_backward_kernels
 from intent.examples.kernels.backward import softmax as softmax_backward_kernels
 from intent.examples.kernels.sparse import csr_spmm, csr_spmv
 from intent.examples.kernels.streaming import attention
@@ -43,6 +44,8 @@ CASES = {
     "csr_spmm": (csr_spmm.csr_spmm, None),
     "csr_spmv": (csr_spmv.csr_spmv, None),
     "softmax_backward": (softmax_backward_kernels.softmax_backward, None),
+    "layer_norm_backward_rows": (layer_norm_backward_kernels.layer_norm_backward_rows, None),
+    "layer_norm_backward_reduce": (layer_norm_backward_kernels.layer_norm_backward_reduce, None),
     # kernels outside the five families: the compile step must refuse them
     "gemm_f32": (gemm_kernels.gemm_f32, None),
 }

@@ -130,6 +130,28 @@ def softmax_backward(probabilities, upstream, out=None):
     return out
 
 
+def layer_norm_backward_rows(x, dy, weight, mean, rstd, dw_partial, db_partial, inverse_features: float, out=None):
+    """Returns dx; accumulates into ``dw_partial`` / ``db_partial`` (InOut) in place."""
+    device = _require_cuda(x, dy, weight, mean, rstd, dw_partial, db_partial)
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=device)
+    _call("b200_layer_norm_backward_rows", device, *_slots(x), *_slots(dy), *_slots(weight), *_slots(mean),
+          *_slots(rstd), *_slots(out), *_slots(dw_partial), *_slots(db_partial), float(inverse_features), _stream(x))
+    return out
+
+
+def layer_norm_backward_reduce(dw_partial, db_partial, dw=None, db=None):
+    device = _require_cuda(dw_partial, db_partial)
+    columns = dw_partial.shape[1]
+    if dw is None:
+        dw = torch.empty((columns,), dtype=torch.float32, device=device)
+    if db is None:
+        db = torch.empty((columns,), dtype=torch.float32, device=device)
+    _call("b200_layer_norm_backward_reduce", device, *_slots(dw_partial), *_slots(db_partial), *_slots(dw), *_slots(db),
+          _stream(dw_partial))
+    return dw, db
+
+
 def csr_spmm_status(device) -> None:
     """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
     device = torch.device(device)

@@ -133,6 +133,29 @@ def softmax_backward_workload(m=4096, n=4097) -> Workload:
     return Workload("softmax_backward", "GB/s", "hbm", 3.0 * m * n * 4, f"softmax backward fp32 {m}x{n}")
 
 
+def layer_norm_backward_inputs(m: int = 4096, n: int = 4096, groups: int = 128, seed: int = 0):
+    """bf16 x, dy, weight with the f32 row statistics of x (epsilon 1e-5) and zeroed bf16
+    partial-sum matrices; the shape is the reference kernel's (kernels/backward/layer_norm.py:5-7)."""
+    rng = np.random.default_rng(seed)
+    x = _f32(rng.standard_normal((m, n), dtype=np.float32)).to(torch.bfloat16)
+    dy = _f32(rng.standard_normal((m, n), dtype=np.float32)).to(torch.bfloat16)
+    weight = _f32(1.0 + 0.1 * rng.standard_normal(n, dtype=np.float32)).to(torch.bfloat16)
+    values = x.float()
+    mean = values.mean(dim=1)
+    rstd = torch.rsqrt(values.var(dim=1, unbiased=False) + 1e-5)
+    dw_partial = torch.zeros((groups, n), dtype=torch.bfloat16)
+    db_partial = torch.zeros((groups, n), dtype=torch.bfloat16)
+    return x, dy, weight, mean, rstd, dw_partial, db_partial, float(np.float32(1.0 / n))
+
+
+def layer_norm_backward_workload(m=4096, n=4096, groups=128) -> Workload:
+    """Row kernel plus the reduction of its partial sums."""
+    rows_kernel = 3.0 * m * n * 2 + 4.0 * groups * n * 2 + n * 2 + m * 8
+    reduce_kernel = 2.0 * groups * n * 2 + 2.0 * n * 4
+    return Workload("layer_norm_backward", "GB/s", "hbm", rows_kernel + reduce_kernel,
+                    f"LayerNorm backward bf16 {m}x{n}, {groups} partial-sum groups (rows + reduce)")
+
+
 def spmv_workload(rows=32768, columns=32768, per_row=32) -> Workload:
     nnz = rows * per_row
     return Workload("spmv", "GB/s", "hbm", float((rows + 1) * 4 + nnz * 8 + columns * 4 + rows * 4),

@@ -174,3 +174,33 @@ def now_ms() -> float:
 
 def evict(buffer: torch.Tensor) -> None:
     library().oracle_evict(_ptr(buffer), _i64(buffer.numel() * buffer.element_size()))
+
+
+def layer_norm_backward_rows(x, dy, weight, mean, rstd, dw_partial, db_partial, inverse_features: float, *,
+                             workers=None):
+    """Returns dx; accumulates into ``dw_partial`` / ``db_partial`` in place (they are InOut)."""
+    _check_cpu(x, dy, weight, mean, rstd, dw_partial, db_partial)
+    for t in (x, dy, dw_partial, db_partial):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise ValueError("the oracle takes bf16 matrices with unit inner strides here")
+    m, n = x.shape
+    dx = torch.empty((m, n), dtype=torch.bfloat16)
+    status = library().oracle_layer_norm_backward_rows(
+        _ptr(x), _ptr(dy), _ptr(weight.contiguous()), _ptr(mean.contiguous()), _ptr(rstd.contiguous()), _ptr(dx),
+        _ptr(dw_partial), _ptr(db_partial), _i64(m), _i64(n), _i64(dw_partial.shape[0]), _i64(x.stride(0)),
+        _i64(dy.stride(0)), _i64(dx.stride(0)), _i64(dw_partial.stride(0)), _i64(db_partial.stride(0)),
+        ctypes.c_float(inverse_features), _i64(workers or default_workers()))
+    if status:
+        raise ValueError("oracle_layer_norm_backward_rows rejected its arguments")
+    return dx
+
+
+def layer_norm_backward_reduce(dw_partial, db_partial, *, workers=None):
+    _check_cpu(dw_partial, db_partial)
+    groups, n = dw_partial.shape
+    dw = torch.empty((n,), dtype=torch.float32)
+    db = torch.empty((n,), dtype=torch.float32)
+    library().oracle_layer_norm_backward_reduce(
+        _ptr(dw_partial), _ptr(db_partial), _ptr(dw), _ptr(db), _i64(groups), _i64(n),
+        _i64(dw_partial.stride(0)), _i64(db_partial.stride(0)), _i64(workers or default_workers()))
+    return dw, db

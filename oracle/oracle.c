@@ -598,6 +598,83 @@ int oracle_softmax_backward(const float *p, const float *u, float *g, int64_t m,
   return ORACLE_OK;
 }
 
+/* layer_norm_backward_rows  kernels/backward/layer_norm.py:12-66 (bf16 operands, f32 arithmetic).
+   scatter_reduce combines repeated addresses with the typed bf16 add and promises no order
+   (doc/dsl/types-numerics-and-effects.en.md:242); this restatement fixes one: the rows of a
+   group (row % groups) in ascending order, each update rounded to bf16.  Work is split over
+   groups so the order does not depend on the team size. */
+struct layer_norm_backward_args {
+  const uint16_t *x, *dy, *weight; const float *mean, *rstd;
+  uint16_t *dx, *dw_partial, *db_partial;
+  int64_t m, n, groups, xs0, dys0, dxs0, dws0, dbs0;
+  float inverse_features;
+};
+static void layer_norm_backward_groups(void *opaque, int64_t begin, int64_t end) {
+  const struct layer_norm_backward_args *a = opaque;
+  for (int64_t g = begin; g < end; ++g) {
+    uint16_t *dw = a->dw_partial + g * a->dws0, *db = a->db_partial + g * a->dbs0;
+    for (int64_t r = g; r < a->m; r += a->groups) {
+      const uint16_t *x = a->x + r * a->xs0, *dy = a->dy + r * a->dys0;
+      uint16_t *dx = a->dx + r * a->dxs0;
+      const float row_mean = a->mean[r], row_rstd = a->rstd[r];
+      float lane[LANES], lane2[LANES];
+      for (int i = 0; i < LANES; ++i) lane[i] = lane2[i] = 0.0f;
+      for (int64_t c = 0; c < a->n; ++c) {
+        const float normalized = (bf16_to_f32(x[c]) - row_mean) * row_rstd;
+        const float weighted_dy = bf16_to_f32(a->weight[c]) * bf16_to_f32(dy[c]);
+        lane[c % LANES] = lane[c % LANES] + weighted_dy;
+        lane2[c % LANES] = lane2[c % LANES] + weighted_dy * normalized;
+      }
+      const float mean_weighted_dy = lanes_sum(lane) * a->inverse_features;
+      const float mean_weighted_dy_normalized = lanes_sum(lane2) * a->inverse_features;
+      for (int64_t c = 0; c < a->n; ++c) {
+        const float dy_value = bf16_to_f32(dy[c]);
+        const float normalized = (bf16_to_f32(x[c]) - row_mean) * row_rstd;
+        const float weighted_dy = bf16_to_f32(a->weight[c]) * dy_value;
+        dx[c] = f32_to_bf16((weighted_dy - mean_weighted_dy - normalized * mean_weighted_dy_normalized) * row_rstd);
+        const float dw_value = bf16_to_f32(f32_to_bf16(dy_value * normalized));
+        dw[c] = f32_to_bf16(bf16_to_f32(dw[c]) + dw_value);
+        db[c] = f32_to_bf16(bf16_to_f32(db[c]) + dy_value);
+      }
+    }
+  }
+}
+int oracle_layer_norm_backward_rows(const uint16_t *x, const uint16_t *dy, const uint16_t *weight, const float *mean,
+                                    const float *rstd, uint16_t *dx, uint16_t *dw_partial, uint16_t *db_partial,
+                                    int64_t m, int64_t n, int64_t groups, int64_t xs0, int64_t dys0, int64_t dxs0,
+                                    int64_t dws0, int64_t dbs0, float inverse_features, int64_t workers) {
+  if (groups <= 0) return ORACLE_BAD_INDEX;
+  struct layer_norm_backward_args a = {x, dy, weight, mean, rstd, dx, dw_partial, db_partial,
+                                       m, n, groups, xs0, dys0, dxs0, dws0, dbs0, inverse_features};
+  dispatch_team(layer_norm_backward_groups, &a, groups, workers);
+  return ORACLE_OK;
+}
+
+/* layer_norm_backward_reduce  kernels/backward/layer_norm.py:69-90: f32 sums of the bf16 partials
+   over the group axis, groups ascending. */
+struct layer_norm_reduce_args {
+  const uint16_t *dw_partial, *db_partial; float *dw, *db;
+  int64_t groups, dws0, dbs0;
+};
+static void layer_norm_reduce_columns(void *opaque, int64_t begin, int64_t end) {
+  const struct layer_norm_reduce_args *a = opaque;
+  for (int64_t c = begin; c < end; ++c) {
+    float dw = 0.0f, db = 0.0f;
+    for (int64_t g = 0; g < a->groups; ++g) {
+      dw = dw + bf16_to_f32(a->dw_partial[g * a->dws0 + c]);
+      db = db + bf16_to_f32(a->db_partial[g * a->dbs0 + c]);
+    }
+    a->dw[c] = dw;
+    a->db[c] = db;
+  }
+}
+int oracle_layer_norm_backward_reduce(const uint16_t *dw_partial, const uint16_t *db_partial, float *dw, float *db,
+                                      int64_t groups, int64_t n, int64_t dws0, int64_t dbs0, int64_t workers) {
+  struct layer_norm_reduce_args a = {dw_partial, db_partial, dw, db, groups, dws0, dbs0};
+  dispatch_team(layer_norm_reduce_columns, &a, n, workers);
+  return ORACLE_OK;
+}
+
 /* ---- timing helper for the CPU baseline --------------------------------- */
 /* Mirrors the CPU provider's benchmark export: the cache-eviction memset sits
    outside the timed interval (runtime/mojo/compilation.py:34, 76-82). */

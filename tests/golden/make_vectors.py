@@ -22,5 +22,11 @@ q, k, v, scale = workloads.attention_inputs(1, 2, 32, 64, seed=103)
 vectors["attention"] = oracle.attention(q, k, v, scale, chunk=16)
 ro, ci, va, x = workloads.csr_inputs(8, 32, 4, 16, seed=104)
 vectors["csr_spmm"] = oracle.csr_spmm(ro, ci, va, x)
+x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(8, 32, 4, seed=105)
+vectors["layer_norm_backward_dx"] = oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, inv)
+vectors["layer_norm_backward_dw_partial"], vectors["layer_norm_backward_db_partial"] = dw_partial, db_partial
+vectors["layer_norm_backward_dw"], vectors["layer_norm_backward_db"] = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
+p, u = workloads.softmax_backward_inputs(4, 20, seed=106)
+vectors["softmax_backward"] = oracle.softmax_backward(p, u)
 torch.save(vectors, Path(__file__).resolve().parent / "oracle_vectors.pt")
 print({k: tuple(v.shape) for k, v in vectors.items()})

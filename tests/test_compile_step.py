@@ -27,6 +27,8 @@ EXPECTED = {
     "csr_spmm": ("csr_spmm", {}),
     "csr_spmv": ("csr_spmv", {}),
     "softmax_backward": ("softmax_backward", {"dtype": 0}),
+    "layer_norm_backward_rows": ("layer_norm_backward_rows", {}),
+    "layer_norm_backward_reduce": ("layer_norm_backward_reduce", {}),
     "csr_spmm_262144": ("csr_spmm", {}),
 }
 

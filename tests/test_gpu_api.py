@@ -125,6 +125,25 @@ def test_backward_pair_registers_with_autograd():
     assert relative_error(full.grad[:64], reference.grad) <= 1e-4
 
 
+def test_layer_norm_backward_pair_through_the_artifact_api():
+    """The InOut partial sums are supplied by the caller and updated in place; dx, dw, db are
+    allocated by the runtime (kernels/backward/layer_norm.py:12-90)."""
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(256, 1024, 128, seed=5)
+    device = [t.to(DEV) for t in (x, dy, w, mean, rstd, dw_partial, db_partial)]
+    rows = b200.jit(b200.kernels.layer_norm_backward_rows).prepare(*device, inv)
+    reduce = b200.jit(b200.kernels.layer_norm_backward_reduce).prepare(device[5], device[6])
+    sequence = b200.PreparedSequence([rows, reduce], outputs=(rows.result(), *reduce.result()))
+    sequence.compile()
+    sequence.launch()
+    torch.cuda.synchronize()
+    dx, dw, db = sequence.result()
+    expected_dx = oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, inv)
+    expected_dw, expected_db = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
+    assert relative_error(dx, expected_dx) <= 1e-2
+    assert torch.equal(device[5].cpu(), dw_partial) and torch.equal(device[6].cpu(), db_partial)
+    assert torch.equal(dw.cpu(), expected_dw) and torch.equal(db.cpu(), expected_db)
+
+
 def test_prepared_sequence_and_explicit_stream():
     (x,) = workloads.softmax_inputs(4096, 4097, seed=8)
     xd = x.to(DEV)

@@ -232,6 +232,33 @@ def test_softmax_backward(m, n):
     assert relative_error(ours, expected) <= 1e-4
 
 
+@pytest.mark.parametrize("m,n,groups", [(256, 512, 128), (130, 4096, 128), (77, 8192, 16), (5, 40, 3), (300, 1000, 128)])
+def test_layer_norm_backward(m, n, groups):
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(m, n, groups, seed=m + n)
+    # InOut: start from non-zero partial sums
+    g = torch.Generator().manual_seed(groups)
+    dw_partial = torch.randn(groups, n, generator=g).to(torch.bfloat16)
+    db_partial = torch.randn(groups, n, generator=g).to(torch.bfloat16)
+    ours_w, ours_b = dw_partial.to(DEV), db_partial.to(DEV)
+    dx = ops.layer_norm_backward_rows(*cuda(x, dy, w, mean, rstd), ours_w, ours_b, inv)
+    expected_dx = oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, inv)
+    assert relative_error(dx, expected_dx) <= 1e-2
+    # the partial sums do not depend on the row reductions: same update order, same roundings
+    assert torch.equal(ours_w.cpu(), dw_partial) and torch.equal(ours_b.cpu(), db_partial)
+    dw, db = ops.layer_norm_backward_reduce(ours_w, ours_b)
+    expected_dw, expected_db = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
+    assert torch.equal(dw.cpu(), expected_dw) and torch.equal(db.cpu(), expected_db)
+
+
+def test_layer_norm_backward_layout_errors():
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(8, 36, 4, seed=1)
+    with pytest.raises(NotImplementedError):                       # N is not a multiple of 8
+        ops.layer_norm_backward_rows(*cuda(x, dy, w, mean, rstd, dw_partial, db_partial), inv)
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(8, 64, 4, seed=1)
+    with pytest.raises(ValueError):                                # group counts disagree
+        ops.layer_norm_backward_rows(*cuda(x, dy, w, mean, rstd, dw_partial, db_partial[:2]), inv)
+
+
 COLUMN_BLOCK_SCRIPT = """
 import sys, torch
 sys.path.insert(0, %r)

@@ -109,6 +109,27 @@ def test_csr_spmv_and_softmax_backward():
     assert relative_error(oracle.softmax_backward(probabilities, upstream), expected) <= 1e-5
 
 
+def test_layer_norm_backward_against_autograd():
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(256, 512, 128, seed=23)
+    dx = oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, inv)
+    dw, db = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
+    xd = x.double().requires_grad_(True)
+    wd = w.double().requires_grad_(True)
+    bd = torch.zeros(512, dtype=torch.double, requires_grad=True)
+    torch.nn.functional.layer_norm(xd, (512,), wd, bd, 1e-5).backward(dy.double())
+    assert relative_error(dx, xd.grad) <= 1e-2            # one bf16 rounding of the result
+    assert relative_error(dw, wd.grad) <= 2e-2            # two bf16-rounded updates per group
+    assert relative_error(db, bd.grad) <= 2e-2
+    # the partial sums are InOut: a second call accumulates on top of the first, and the team size
+    # does not change the result (the update order is fixed per group)
+    again_w, again_b = dw_partial.clone(), db_partial.clone()
+    oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, again_w, again_b, inv, workers=3)
+    fresh_w, fresh_b = torch.zeros_like(again_w), torch.zeros_like(again_b)
+    oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, fresh_w, fresh_b, inv, workers=1)
+    assert torch.equal(fresh_w, dw_partial) and torch.equal(fresh_b, db_partial)
+    assert not torch.equal(again_w, dw_partial)
+
+
 def test_committed_vectors():
     vectors = torch.load(GOLDEN)
     (x,) = workloads.softmax_inputs(4, 16, seed=100)
@@ -121,3 +142,12 @@ def test_committed_vectors():
     assert torch.equal(oracle.attention(q, k, v, scale, chunk=16), vectors["attention"])
     ro, ci, va, x = workloads.csr_inputs(8, 32, 4, 16, seed=104)
     assert torch.equal(oracle.csr_spmm(ro, ci, va, x), vectors["csr_spmm"])
+    x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(8, 32, 4, seed=105)
+    assert torch.equal(oracle.layer_norm_backward_rows(x, dy, w, mean, rstd, dw_partial, db_partial, inv),
+                       vectors["layer_norm_backward_dx"])
+    assert torch.equal(dw_partial, vectors["layer_norm_backward_dw_partial"])
+    assert torch.equal(db_partial, vectors["layer_norm_backward_db_partial"])
+    dw, db = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
+    assert torch.equal(dw, vectors["layer_norm_backward_dw"]) and torch.equal(db, vectors["layer_norm_backward_db"])
+    p, u = workloads.softmax_backward_inputs(4, 20, seed=106)
+    assert torch.equal(oracle.softmax_backward(p, u), vectors["softmax_backward"])
