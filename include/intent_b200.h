@@ -125,6 +125,60 @@ int b200_layer_norm_backward_reduce(const void *dw_partial, int64_t dw_d0, int64
                                     void *stream);
 
 /*
+ * Attention backward, three kernels (f16 / bf16 operands, f32 arithmetic, natural-log LSE; views are
+ * (batch, head, sequence, D) with unit innermost stride, D in {64, 128}).  They replace
+ * attention_backward_delta, attention_backward_dkdv and attention_backward_dq
+ * (python/intent/examples/kernels/backward/attention.py:16-33, 91-137, 171-211), which
+ * python/intent/examples/programs/attention_backward.py:19-41 runs in this order.
+ *   delta[b,h,q] = sum_d f32(output) * f32(grad_output)
+ *   P = exp2(S * scale*log2e - lse*log2e), excluded pairs (key > query when causal) are 0
+ *   dS = P * (dO . V^T - delta);  grad_v = f16(P)^T . dO;  grad_k = scale * f16(dS)^T . Q;
+ *   grad_q = scale * f16(dS) . K
+ * q, k, v, grad_output go through TMA: 16-byte aligned bases, outer strides multiples of 8
+ * elements.  The gradient entries take the same B200_WORKSPACE_WORDS workspace view as
+ * b200_flash_attention, then the int32 tail dtype, head_group, causal.
+ */
+int b200_attention_backward_delta(
+        const void *output, int64_t output_d0, int64_t output_d1, int64_t output_d2, int64_t output_d3,
+        int64_t output_s0, int64_t output_s1, int64_t output_s2, int64_t output_s3,
+        const void *grad_output, int64_t grad_output_d0, int64_t grad_output_d1, int64_t grad_output_d2, int64_t grad_output_d3,
+        int64_t grad_output_s0, int64_t grad_output_s1, int64_t grad_output_s2, int64_t grad_output_s3,
+        void *delta, int64_t delta_d0, int64_t delta_d1, int64_t delta_d2, int64_t delta_s0, int64_t delta_s1, int64_t delta_s2,
+        int32_t dtype, void *stream);
+int b200_attention_backward_dkdv(
+        const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
+        int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,
+        const void *k, int64_t k_d0, int64_t k_d1, int64_t k_d2, int64_t k_d3,
+        int64_t k_s0, int64_t k_s1, int64_t k_s2, int64_t k_s3,
+        const void *v, int64_t v_d0, int64_t v_d1, int64_t v_d2, int64_t v_d3,
+        int64_t v_s0, int64_t v_s1, int64_t v_s2, int64_t v_s3,
+        const void *grad_output, int64_t grad_output_d0, int64_t grad_output_d1, int64_t grad_output_d2, int64_t grad_output_d3,
+        int64_t grad_output_s0, int64_t grad_output_s1, int64_t grad_output_s2, int64_t grad_output_s3,
+        const void *lse, int64_t lse_d0, int64_t lse_d1, int64_t lse_d2, int64_t lse_s0, int64_t lse_s1, int64_t lse_s2,
+        const void *delta, int64_t delta_d0, int64_t delta_d1, int64_t delta_d2, int64_t delta_s0, int64_t delta_s1, int64_t delta_s2,
+        void *grad_k, int64_t grad_k_d0, int64_t grad_k_d1, int64_t grad_k_d2, int64_t grad_k_d3,
+        int64_t grad_k_s0, int64_t grad_k_s1, int64_t grad_k_s2, int64_t grad_k_s3,
+        void *grad_v, int64_t grad_v_d0, int64_t grad_v_d1, int64_t grad_v_d2, int64_t grad_v_d3,
+        int64_t grad_v_s0, int64_t grad_v_s1, int64_t grad_v_s2, int64_t grad_v_s3,
+        float scale, void *workspace, int64_t ws_d0, int64_t ws_s0, int32_t dtype, int32_t head_group, int32_t causal,
+        void *stream);
+int b200_attention_backward_dq(
+        const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
+        int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,
+        const void *k, int64_t k_d0, int64_t k_d1, int64_t k_d2, int64_t k_d3,
+        int64_t k_s0, int64_t k_s1, int64_t k_s2, int64_t k_s3,
+        const void *v, int64_t v_d0, int64_t v_d1, int64_t v_d2, int64_t v_d3,
+        int64_t v_s0, int64_t v_s1, int64_t v_s2, int64_t v_s3,
+        const void *grad_output, int64_t grad_output_d0, int64_t grad_output_d1, int64_t grad_output_d2, int64_t grad_output_d3,
+        int64_t grad_output_s0, int64_t grad_output_s1, int64_t grad_output_s2, int64_t grad_output_s3,
+        const void *lse, int64_t lse_d0, int64_t lse_d1, int64_t lse_d2, int64_t lse_s0, int64_t lse_s1, int64_t lse_s2,
+        const void *delta, int64_t delta_d0, int64_t delta_d1, int64_t delta_d2, int64_t delta_s0, int64_t delta_s1, int64_t delta_s2,
+        void *grad_q, int64_t grad_q_d0, int64_t grad_q_d1, int64_t grad_q_d2, int64_t grad_q_d3,
+        int64_t grad_q_s0, int64_t grad_q_s1, int64_t grad_q_s2, int64_t grad_q_s3,
+        float scale, void *workspace, int64_t ws_d0, int64_t ws_s0, int32_t dtype, int32_t head_group, int32_t causal,
+        void *stream);
+
+/*
  * LayerNorm forward.  Replaces layer_norm_f16 / layer_norm_bf16 (centred
  * two-pass variance) and weighted_layer_norm (f32, E[x^2] - mean^2)
  * (python/intent/examples/kernels/normalization/layer_norm.py:9-85).

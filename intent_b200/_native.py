@@ -42,6 +42,9 @@ SIGNATURES = {
     "b200_softmax_backward": _view(2) * 3 + [_I32, _P],
     "b200_layer_norm_backward_rows": _view(2) * 2 + _view(1) * 3 + _view(2) * 3 + [_F32, _P],
     "b200_layer_norm_backward_reduce": _view(2) * 2 + _view(1) * 2 + [_P],
+    "b200_attention_backward_delta": _view(4) * 2 + _view(3) + [_I32, _P],
+    "b200_attention_backward_dkdv": _view(4) * 4 + _view(3) * 2 + _view(4) * 2 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
+    "b200_attention_backward_dq": _view(4) * 4 + _view(3) * 2 + _view(4) + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
     "b200_csr_spmm_status": [ctypes.POINTER(_I64), _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],

@@ -22,6 +22,7 @@ import sys
 import intent
 from intent.examples.kernels.contraction import gemm as gemm_kernels
 from intent.examples.kernels.normalization import layer_norm, softmax
+from intent.examples.kernels.backward import attention as attention_backward_kernels
 from intent.examples.kernels.backward import layer_norm as layer_norm_backward_kernels
 from intent.examples.kernels.backward import softmax as softmax_backward_kernels
 from intent.examples.kernels.sparse import csr_spmm, csr_spmv
@@ -46,6 +47,13 @@ CASES = {
     "softmax_backward": (softmax_backward_kernels.softmax_backward, None),
     "layer_norm_backward_rows": (layer_norm_backward_kernels.layer_norm_backward_rows, None),
     "layer_norm_backward_reduce": (layer_norm_backward_kernels.layer_norm_backward_reduce, None),
+    "attention_backward_delta": (attention_backward_kernels.attention_backward_delta, None),
+    "attention_backward_dkdv": (attention_backward_kernels.attention_backward_dkdv, {"HEAD_GROUP": 4, "CAUSAL": True}),
+    "attention_backward_dkdv_noncausal": (attention_backward_kernels.attention_backward_dkdv,
+                                          {"HEAD_GROUP": 1, "CAUSAL": False}),
+    "attention_backward_dq": (attention_backward_kernels.attention_backward_dq, {"HEAD_GROUP": 4, "CAUSAL": True}),
+    "attention_backward_dq_noncausal": (attention_backward_kernels.attention_backward_dq,
+                                        {"HEAD_GROUP": 1, "CAUSAL": False}),
     # kernels outside the five families: the compile step must refuse them
     "gemm_f32": (gemm_kernels.gemm_f32, None),
 }

@@ -152,6 +152,38 @@ def layer_norm_backward_reduce(dw_partial, db_partial, dw=None, db=None):
     return dw, db
 
 
+def attention_backward_delta(output, grad_output, out=None):
+    device = _require_cuda(output, grad_output)
+    if out is None:
+        out = torch.empty(output.shape[:3], dtype=torch.float32, device=device)
+    _call("b200_attention_backward_delta", device, *_slots(output), *_slots(grad_output), *_slots(out),
+          _CODES[output.dtype], _stream(output))
+    return out
+
+
+def attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
+                            causal: bool = True, grad_k=None, grad_v=None):
+    device = _require_cuda(q, k, v, grad_output, lse, delta)
+    grad_k = torch.empty(k.shape, dtype=k.dtype, device=device) if grad_k is None else grad_k
+    grad_v = torch.empty(v.shape, dtype=v.dtype, device=device) if grad_v is None else grad_v
+    space = workspace(device)
+    _call("b200_attention_backward_dkdv", device, *_slots(q), *_slots(k), *_slots(v), *_slots(grad_output),
+          *_slots(lse), *_slots(delta), *_slots(grad_k), *_slots(grad_v), float(scale), *_slots(space),
+          _CODES[q.dtype], int(head_group), int(causal), _stream(q))
+    return grad_k, grad_v
+
+
+def attention_backward_dq(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
+                          causal: bool = True, grad_q=None):
+    device = _require_cuda(q, k, v, grad_output, lse, delta)
+    grad_q = torch.empty(q.shape, dtype=q.dtype, device=device) if grad_q is None else grad_q
+    space = workspace(device)
+    _call("b200_attention_backward_dq", device, *_slots(q), *_slots(k), *_slots(v), *_slots(grad_output),
+          *_slots(lse), *_slots(delta), *_slots(grad_q), float(scale), *_slots(space), _CODES[q.dtype],
+          int(head_group), int(causal), _stream(q))
+    return grad_q
+
+
 def csr_spmm_status(device) -> None:
     """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
     device = torch.device(device)

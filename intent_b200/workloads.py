@@ -59,6 +59,28 @@ def attention_inputs(b: int = 8, h: int = 32, s: int = 4096, d: int = 128, seed:
     return q, k, v, float(np.float32(1.0 / math.sqrt(d)))
 
 
+def attention_backward_inputs(b: int = 2, hq: int = 8, hk: int = 2, s: int = 1024, d: int = 64, seed: int = 0,
+                              dtype=torch.float16, causal: bool = True, keys: int | None = None):
+    """q, k, v, output, grad_output, lse (natural log), scale for the backward trio; the forward
+    pass that yields output and lse is evaluated in f64 on the rounded operands.  Defaults are the
+    reference kernels' shape (kernels/backward/attention.py:7-13)."""
+    rng = np.random.default_rng(seed)
+    sk = s if keys is None else keys
+    q = _f32(0.5 * rng.standard_normal((b, hq, s, d), dtype=np.float32)).to(dtype)
+    k = _f32(0.5 * rng.standard_normal((b, hk, sk, d), dtype=np.float32)).to(dtype)
+    v = _f32(0.5 * rng.standard_normal((b, hk, sk, d), dtype=np.float32)).to(dtype)
+    grad_output = _f32(0.5 * rng.standard_normal((b, hq, s, d), dtype=np.float32)).to(dtype)
+    scale = float(np.float32(1.0 / math.sqrt(d)))
+    group = hq // hk
+    scores = torch.einsum("bhqd,bhkd->bhqk", q.double(), k.double().repeat_interleave(group, dim=1)) * scale
+    if causal:
+        allowed = torch.arange(sk)[None, :] <= torch.arange(s)[:, None]
+        scores = scores.masked_fill(~allowed, float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    output = torch.einsum("bhqk,bhkd->bhqd", torch.exp(scores - lse[..., None]), v.double().repeat_interleave(group, dim=1))
+    return q, k, v, output.to(dtype), grad_output, lse.float(), scale
+
+
 def csr_inputs(rows: int = 262144, columns: int = 262144, per_row: int = 32, features: int = 128,
                seed: int = 0):
     """`per_row` distinct, ascending, uniformly drawn column indices per row."""

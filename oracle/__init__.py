@@ -204,3 +204,52 @@ def layer_norm_backward_reduce(dw_partial, db_partial, *, workers=None):
         _ptr(dw_partial), _ptr(db_partial), _ptr(dw), _ptr(db), _i64(groups), _i64(n),
         _i64(dw_partial.stride(0)), _i64(db_partial.stride(0)), _i64(workers or default_workers()))
     return dw, db
+
+
+def _strides3(t: torch.Tensor):
+    return list(t.stride()[:3])
+
+
+def attention_backward_delta(output, grad_output, *, workers=None):
+    _check_cpu(output, grad_output)
+    b, hq, sq, d = output.shape
+    delta = torch.empty((b, hq, sq), dtype=torch.float32)
+    library().oracle_attention_backward_delta(
+        _ptr(output), _ptr(grad_output), _ptr(delta), _i64(b), _i64(hq), _i64(sq), _i64(d),
+        (ctypes.c_int64 * 3)(*_strides3(output)), (ctypes.c_int64 * 3)(*_strides3(grad_output)),
+        (ctypes.c_int64 * 3)(*delta.stride()), _DTYPES[output.dtype], _i64(workers or default_workers()))
+    return delta
+
+
+def _attention_backward(which, q, k, v, grad_output, lse, delta, scale, head_group, causal, workers):
+    _check_cpu(q, k, v, grad_output, lse, delta)
+    for t in (q, k, v, grad_output):
+        if t.stride(3) != 1:
+            raise ValueError("the oracle takes unit inner strides here")
+    b, hq, sq, d = q.shape
+    hk, sk = k.shape[1], k.shape[2]
+    gq = torch.empty((b, hq, sq, d), dtype=q.dtype)
+    gk = torch.empty((b, hk, sk, d), dtype=q.dtype)
+    gv = torch.empty((b, hk, sk, d), dtype=q.dtype)
+    strides = []
+    for t in (q, k, v, grad_output, lse, delta, gq, gk, gv):
+        strides += _strides3(t)
+    status = library().oracle_attention_backward(
+        which, _ptr(q), _ptr(k), _ptr(v), _ptr(grad_output), _ptr(lse), _ptr(delta), _ptr(gq), _ptr(gk), _ptr(gv),
+        _i64(b), _i64(hq), _i64(hk), _i64(sq), _i64(sk), _i64(d), (ctypes.c_int64 * 27)(*strides),
+        ctypes.c_float(scale), _i64(head_group), int(causal), _DTYPES[q.dtype], _i64(workers or default_workers()))
+    if status:
+        raise ValueError("oracle_attention_backward rejected its arguments")
+    return gq, gk, gv
+
+
+def attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
+                            causal: bool = True, workers=None):
+    _, gk, gv = _attention_backward(0, q, k, v, grad_output, lse, delta, scale, head_group, causal, workers)
+    return gk, gv
+
+
+def attention_backward_dq(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
+                          causal: bool = True, workers=None):
+    gq, _, _ = _attention_backward(1, q, k, v, grad_output, lse, delta, scale, head_group, causal, workers)
+    return gq

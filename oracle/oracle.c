@@ -675,6 +675,166 @@ int oracle_layer_norm_backward_reduce(const uint16_t *dw_partial, const uint16_t
   return ORACLE_OK;
 }
 
+/* ======================================================================== */
+/* attention backward trio  kernels/backward/attention.py (f16 operands, f32 arithmetic,
+   natural-log LSE).  Views are (batch, head, sequence, D) with unit inner stride; strides are
+   given in elements for the three outer axes. */
+
+/* attention_backward_delta  attention.py:16-33: delta = reduce.sum(f32(O) * f32(dO), axis=D). */
+struct delta_args {
+  const uint16_t *o, *go; float *delta;
+  int64_t hq, sq, d, os[3], gs[3], ds[3];
+  int dtype;
+};
+static void delta_units(void *opaque, int64_t begin, int64_t end) {
+  const struct delta_args *a = opaque;
+  for (int64_t unit = begin; unit < end; ++unit) {
+    const int64_t b = unit / a->hq, h = unit % a->hq;
+    for (int64_t q = 0; q < a->sq; ++q) {
+      const uint16_t *o = a->o + b * a->os[0] + h * a->os[1] + q * a->os[2];
+      const uint16_t *g = a->go + b * a->gs[0] + h * a->gs[1] + q * a->gs[2];
+      float lane[LANES];
+      for (int i = 0; i < LANES; ++i) lane[i] = 0.0f;
+      for (int64_t c = 0; c < a->d; ++c)
+        lane[c % LANES] = lane[c % LANES] + half_to_f32(o[c], a->dtype) * half_to_f32(g[c], a->dtype);
+      a->delta[b * a->ds[0] + h * a->ds[1] + q * a->ds[2]] = lanes_sum(lane);
+    }
+  }
+}
+int oracle_attention_backward_delta(const uint16_t *o, const uint16_t *go, float *delta, int64_t batch, int64_t hq,
+                                    int64_t sq, int64_t d, const int64_t *os, const int64_t *gs, const int64_t *ds,
+                                    int dtype, int64_t workers) {
+  struct delta_args a = {.o = o, .go = go, .delta = delta, .hq = hq, .sq = sq, .d = d, .dtype = dtype};
+  memcpy(a.os, os, sizeof a.os); memcpy(a.gs, gs, sizeof a.gs); memcpy(a.ds, ds, sizeof a.ds);
+  dispatch_team(delta_units, &a, batch * hq, workers);
+  return ORACLE_OK;
+}
+
+struct attention_backward_args {
+  const uint16_t *q, *k, *v, *go; const float *lse, *delta;
+  uint16_t *gq, *gk, *gv;
+  int64_t hq, hk, sq, sk, d, head_group;
+  int64_t qs[3], ks[3], vs[3], gos[3], ls[3], dls[3], gqs[3], gks[3], gvs[3];
+  float scale; int causal, dtype;
+};
+static inline uint16_t narrow_half(float f, int dtype) { return dtype == DT_F16 ? f32_to_f16(f) : f32_to_bf16(f); }
+
+/* One (query row, key row) pair of summarize_key_value_gradients / summarize_query_gradients
+   (attention.py:47-84, 139-163): probability and grad_scores, both already rounded through f16
+   where the reference casts them for the second pair of products. */
+static inline void gradient_pair(const struct attention_backward_args *a, const float *qrow, const float *krow,
+                                 const float *vrow, const float *grow, float lse, float delta, int valid,
+                                 float *probability16, float *grad_scores16) {
+  const float log2e = (float)1.4426950408889634;
+  float score = 0.0f, grad_probability = 0.0f;
+  for (int64_t c = 0; c < a->d; ++c) score = score + qrow[c] * krow[c];
+  for (int64_t c = 0; c < a->d; ++c) grad_probability = grad_probability + grow[c] * vrow[c];
+  float probability = exp2f(score * (a->scale * log2e) - lse * log2e);
+  if (!valid) probability = 0.0f;
+  const float grad_scores = probability * (grad_probability - delta);
+  *probability16 = round_through_half(probability, a->dtype);
+  *grad_scores16 = valid ? round_through_half(grad_scores, a->dtype) : 0.0f;
+}
+
+static float *widen_rows(const uint16_t *base, int64_t rows, int64_t d, int64_t stride, int dtype) {
+  float *out = malloc((size_t)(rows > 0 ? rows : 1) * d * sizeof(float));
+  if (!out) return NULL;
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t c = 0; c < d; ++c) out[r * d + c] = half_to_f32(base[r * stride + c], dtype);
+  return out;
+}
+
+/* attention_backward_dkdv  attention.py:91-137: one unit per (batch, key head); the fold runs over
+   the HEAD_GROUP * Q member queries of the group in ascending member order. */
+static void dkdv_units(void *opaque, int64_t begin, int64_t end) {
+  const struct attention_backward_args *a = opaque;
+  const int64_t D = a->d;
+  for (int64_t unit = begin; unit < end; ++unit) {
+    const int64_t b = unit / a->hk, hk = unit % a->hk;
+    float *kf = widen_rows(a->k + b * a->ks[0] + hk * a->ks[1], a->sk, D, a->ks[2], a->dtype);
+    float *vf = widen_rows(a->v + b * a->vs[0] + hk * a->vs[1], a->sk, D, a->vs[2], a->dtype);
+    float *gk = calloc((size_t)(a->sk > 0 ? a->sk : 1) * D, sizeof(float));
+    float *gv = calloc((size_t)(a->sk > 0 ? a->sk : 1) * D, sizeof(float));
+    float *qrow = malloc(D * sizeof(float)), *grow = malloc(D * sizeof(float));
+    if (kf && vf && gk && gv && qrow && grow) {
+      for (int64_t member = 0; member < a->head_group * a->sq; ++member) {
+        const int64_t hq = hk * a->head_group + member / a->sq, qi = member % a->sq;
+        const uint16_t *q = a->q + b * a->qs[0] + hq * a->qs[1] + qi * a->qs[2];
+        const uint16_t *g = a->go + b * a->gos[0] + hq * a->gos[1] + qi * a->gos[2];
+        for (int64_t c = 0; c < D; ++c) { qrow[c] = half_to_f32(q[c], a->dtype); grow[c] = half_to_f32(g[c], a->dtype); }
+        const float lse = a->lse[b * a->ls[0] + hq * a->ls[1] + qi * a->ls[2]];
+        const float delta = a->delta[b * a->dls[0] + hq * a->dls[1] + qi * a->dls[2]];
+        const int64_t keys = a->causal ? (qi + 1 < a->sk ? qi + 1 : a->sk) : a->sk;   /* key <= query */
+        for (int64_t ki = 0; ki < keys; ++ki) {
+          float p16, gs16;
+          gradient_pair(a, qrow, kf + ki * D, vf + ki * D, grow, lse, delta, 1, &p16, &gs16);
+          for (int64_t c = 0; c < D; ++c) {
+            gv[ki * D + c] = gv[ki * D + c] + p16 * grow[c];
+            gk[ki * D + c] = gk[ki * D + c] + gs16 * qrow[c];
+          }
+        }
+      }
+      for (int64_t ki = 0; ki < a->sk; ++ki) {
+        uint16_t *ok = a->gk + b * a->gks[0] + hk * a->gks[1] + ki * a->gks[2];
+        uint16_t *ov = a->gv + b * a->gvs[0] + hk * a->gvs[1] + ki * a->gvs[2];
+        for (int64_t c = 0; c < D; ++c) {
+          ok[c] = narrow_half(gk[ki * D + c] * a->scale, a->dtype);
+          ov[c] = narrow_half(gv[ki * D + c], a->dtype);
+        }
+      }
+    }
+    free(kf); free(vf); free(gk); free(gv); free(qrow); free(grow);
+  }
+}
+
+/* attention_backward_dq  attention.py:171-211: one unit per (batch, query head), keys ascending. */
+static void dq_units(void *opaque, int64_t begin, int64_t end) {
+  const struct attention_backward_args *a = opaque;
+  const int64_t D = a->d;
+  for (int64_t unit = begin; unit < end; ++unit) {
+    const int64_t b = unit / a->hq, hq = unit % a->hq, hk = hq / a->head_group;
+    float *kf = widen_rows(a->k + b * a->ks[0] + hk * a->ks[1], a->sk, D, a->ks[2], a->dtype);
+    float *vf = widen_rows(a->v + b * a->vs[0] + hk * a->vs[1], a->sk, D, a->vs[2], a->dtype);
+    float *qrow = malloc(D * sizeof(float)), *grow = malloc(D * sizeof(float)), *acc = malloc(D * sizeof(float));
+    if (kf && vf && qrow && grow && acc) {
+      for (int64_t qi = 0; qi < a->sq; ++qi) {
+        const uint16_t *q = a->q + b * a->qs[0] + hq * a->qs[1] + qi * a->qs[2];
+        const uint16_t *g = a->go + b * a->gos[0] + hq * a->gos[1] + qi * a->gos[2];
+        for (int64_t c = 0; c < D; ++c) { qrow[c] = half_to_f32(q[c], a->dtype); grow[c] = half_to_f32(g[c], a->dtype); acc[c] = 0.0f; }
+        const float lse = a->lse[b * a->ls[0] + hq * a->ls[1] + qi * a->ls[2]];
+        const float delta = a->delta[b * a->dls[0] + hq * a->dls[1] + qi * a->dls[2]];
+        const int64_t keys = a->causal ? (qi + 1 < a->sk ? qi + 1 : a->sk) : a->sk;
+        for (int64_t ki = 0; ki < keys; ++ki) {
+          float p16, gs16;
+          gradient_pair(a, qrow, kf + ki * D, vf + ki * D, grow, lse, delta, 1, &p16, &gs16);
+          for (int64_t c = 0; c < D; ++c) acc[c] = acc[c] + gs16 * kf[ki * D + c];
+        }
+        uint16_t *out = a->gq + b * a->gqs[0] + hq * a->gqs[1] + qi * a->gqs[2];
+        for (int64_t c = 0; c < D; ++c) out[c] = narrow_half(acc[c] * a->scale, a->dtype);
+      }
+    }
+    free(kf); free(vf); free(qrow); free(grow); free(acc);
+  }
+}
+
+/* which: 0 = dkdv (writes gk, gv), 1 = dq (writes gq).  strides: nine triples in the order
+   q, k, v, grad_output, lse, delta, grad_q, grad_k, grad_v. */
+int oracle_attention_backward(int which, const uint16_t *q, const uint16_t *k, const uint16_t *v, const uint16_t *go,
+                              const float *lse, const float *delta, uint16_t *gq, uint16_t *gk, uint16_t *gv,
+                              int64_t batch, int64_t hq, int64_t hk, int64_t sq, int64_t sk, int64_t d,
+                              const int64_t *strides, float scale, int64_t head_group, int causal, int dtype,
+                              int64_t workers) {
+  if (head_group <= 0 || hq != hk * head_group) return ORACLE_BAD_INDEX;
+  struct attention_backward_args a = {.q = q, .k = k, .v = v, .go = go, .lse = lse, .delta = delta, .gq = gq,
+                                      .gk = gk, .gv = gv, .hq = hq, .hk = hk, .sq = sq, .sk = sk, .d = d,
+                                      .head_group = head_group, .scale = scale, .causal = causal, .dtype = dtype};
+  int64_t *targets[9] = {a.qs, a.ks, a.vs, a.gos, a.ls, a.dls, a.gqs, a.gks, a.gvs};
+  for (int i = 0; i < 9; ++i) memcpy(targets[i], strides + 3 * i, 3 * sizeof(int64_t));
+  if (which == 0) dispatch_team(dkdv_units, &a, batch * hk, workers);
+  else dispatch_team(dq_units, &a, batch * hq, workers);
+  return ORACLE_OK;
+}
+
 /* ---- timing helper for the CPU baseline --------------------------------- */
 /* Mirrors the CPU provider's benchmark export: the cache-eviction memset sits
    outside the timed interval (runtime/mojo/compilation.py:34, 76-82). */
