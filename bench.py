@@ -48,7 +48,8 @@ NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/.
 NCU_TRAFFIC_BYTES = {"softmax": 16791040, "layer_norm": 221244672, "gemm": 1154501120, "attention": 1057477120,
-                     "spmm": 975351808, "softmax_backward": 161898752, "spmv": 8655872, "layer_norm_backward": None}
+                     "spmm": 975351808, "softmax_backward": 161898752, "spmv": 8655872, "layer_norm_backward": None,
+                     "attention_backward": None}
 
 
 def peaks() -> tuple[dict, str]:
@@ -441,9 +442,67 @@ class LayerNormBackwardCase(Case):
         return run, 1.0, "full workload (4096 rows, rows + reduce)"
 
 
+class AttentionBackwardCase(Case):
+    """delta, dK/dV and dQ (three launches per step)."""
+    name = "attention_backward"
+    launches_per_step = 3
+
+    def __init__(self, device):
+        super().__init__(device)
+        import intent_b200 as b200
+        from intent_b200 import ops
+        self.ops, self.workload = ops, self.workloads.attention_backward_workload()
+        q, k, v, output, grad_output, lse, self.scale = self.workloads.attention_backward_inputs(
+            8, 32, 8, 2048, 128, device=device)
+        self.host = (q, k, v, output, grad_output, lse)
+        self.dev = [t.to(device) for t in self.host]
+        self.delta = torch.empty_like(self.dev[5])
+        self.grads = [torch.empty_like(self.dev[0]), torch.empty_like(self.dev[1]), torch.empty_like(self.dev[2])]
+        self.flush = "inputs larger than L2 (503 MB of operands and gradients per step vs 126 MB)"
+        options = {"HEAD_GROUP": 4, "CAUSAL": True}
+        self.host_in = [pinned(t) for t in self.host]
+        self.dev_in = [torch.empty_like(t) for t in self.dev]
+        qd, kd, vd, od, gd, ld = self.dev_in
+        self.delta_call = b200.jit(b200.kernels.attention_backward_delta).prepare(od, gd)
+        common = (qd, kd, vd, gd, ld, self.delta_call.result(), self.scale)
+        self.dkdv_call = b200.jit(b200.kernels.attention_backward_dkdv, constexprs=options).prepare(*common)
+        self.dq_call = b200.jit(b200.kernels.attention_backward_dq, constexprs=options).prepare(*common)
+        self.host_out = [torch.empty_like(t).pin_memory() for t in (q, k, v)]
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+
+    def launch(self, step):
+        q, k, v, output, grad_output, lse = self.dev
+        self.ops.attention_backward_delta(output, grad_output, out=self.delta)
+        self.ops.attention_backward_dkdv(q, k, v, grad_output, lse, self.delta, self.scale, head_group=4,
+                                         grad_k=self.grads[1], grad_v=self.grads[2])
+        self.ops.attention_backward_dq(q, k, v, grad_output, lse, self.delta, self.scale, head_group=4,
+                                       grad_q=self.grads[0])
+
+    def e2e(self, step):
+        for dev, host in zip(self.dev_in, self.host_in):
+            dev.copy_(host, non_blocking=True)
+        self.delta_call.launch()
+        self.dkdv_call.launch()
+        self.dq_call.launch()
+        grad_k, grad_v = self.dkdv_call.result()
+        for host, dev in zip(self.host_out, (self.dq_call.result(), grad_k, grad_v)):
+            host.copy_(dev, non_blocking=True)
+
+    def cpu(self, oracle, workers):
+        # batch 0, key head 0 with its four query heads: 1 of the 64 (batch, key head) groups
+        q, k, v, output, grad_output, lse = (t[:1, :4] if t.shape[1] == 32 else t[:1, :1] for t in self.host)
+
+        def run():
+            delta = oracle.attention_backward_delta(output, grad_output, workers=workers)
+            oracle.attention_backward_dkdv(q, k, v, grad_output, lse, delta, self.scale, head_group=4, workers=workers)
+            oracle.attention_backward_dq(q, k, v, grad_output, lse, delta, self.scale, head_group=4, workers=workers)
+        return run, 1.0 / 64, "1 of 64 (batch, key head) groups (4 query heads), full sequence"
+
+
 CASES = {"softmax": SoftmaxCase, "layer_norm": LayerNormCase, "gemm": GemmCase, "attention": AttentionCase,
          "spmm": SpmmCase, "softmax_backward": SoftmaxBackwardCase, "spmv": SpmvCase,
-         "layer_norm_backward": LayerNormBackwardCase}
+         "layer_norm_backward": LayerNormBackwardCase, "attention_backward": AttentionBackwardCase}
 
 
 # --------------------------------------------------------------------------- timing
@@ -687,7 +746,8 @@ def main() -> None:
         "warmup": arguments.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
         "dtype": {"softmax": "f32", "layer_norm": "f16", "gemm": "f16", "attention": "bf16", "spmm": "f32",
-                  "softmax_backward": "f32", "spmv": "f32", "layer_norm_backward": "bf16"}[primary],
+                  "softmax_backward": "f32", "spmv": "f32", "layer_norm_backward": "bf16",
+                  "attention_backward": "f16"}[primary],
         "data": "synthetic",
         "config": {"workload": head["workload"], "l2": head["l2"],
                    "parallelism": f"{world} independent shard(s), no data-path collective"},

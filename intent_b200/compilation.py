@@ -138,6 +138,15 @@ class kernels:
     layer_norm_backward_rows = KernelDefinition("layer_norm_backward_rows", (((), "layer_norm_backward_rows.mlir"),))
     layer_norm_backward_reduce = KernelDefinition("layer_norm_backward_reduce",
                                                   (((), "layer_norm_backward_reduce.mlir"),))
+    attention_backward_delta = KernelDefinition("attention_backward_delta", (((), "attention_backward_delta.mlir"),))
+    attention_backward_dkdv = KernelDefinition(
+        "attention_backward_dkdv", (((("CAUSAL", True), ("HEAD_GROUP", 4)), "attention_backward_dkdv.mlir"),
+                                    ((("CAUSAL", False), ("HEAD_GROUP", 1)), "attention_backward_dkdv_noncausal.mlir")),
+        ("HEAD_GROUP", "CAUSAL"))
+    attention_backward_dq = KernelDefinition(
+        "attention_backward_dq", (((("CAUSAL", True), ("HEAD_GROUP", 4)), "attention_backward_dq.mlir"),
+                                  ((("CAUSAL", False), ("HEAD_GROUP", 1)), "attention_backward_dq_noncausal.mlir")),
+        ("HEAD_GROUP", "CAUSAL"))
     csr_spmm = KernelDefinition("csr_spmm", (((), "csr_spmm.mlir"),))
     csr_spmm_262144 = KernelDefinition("csr_spmm", (((), "csr_spmm_262144.mlir"),))
 

@@ -330,6 +330,53 @@ Plan classify(const std::vector<Parameter> &all, const std::vector<Operation> &o
   Plan plan;
   const bool heavy = c.of("contract") || c.of("region_fold") || c.of("for") || c.of("scan") || c.of("region_scan");
 
+  if (c.of("region_fold") == 1 && c.of("view_load") == 6 && c.of("unary<exp2>") == 1 && c.of("binary<true_divide>") == 0) {
+    // ---- attention backward: dK/dV (two outputs, a record summary) or dQ (one output) ----------
+    const bool key_value = c.of("view_store") == 2;
+    const bool causal = c.of("compare") == 1;
+    require(c.of("parallel") == 2 && c.of("unary") == 1 && c.of("transpose") == 2 && c.of("for") == 0 &&
+                c.of("compare") <= 1 && (key_value ? c.of("make_record") == 4 : c.of("view_store") == 1 && c.of("make_record") == 0),
+            "region_fold program is not an attention gradient summary");
+    // causal programs replace the second pair of contractions by masked products with a reduction
+    if (key_value) require(causal ? c.of("contract") == 2 && c.of("mask") == 3 && c.of("reduce") == 2
+                                  : c.of("contract") == 4 && c.of("mask") == 0 && c.of("reduce") == 0,
+                           "dK/dV summary is not K.Q^T, V.dO^T and the two gradient products");
+    else require(causal ? c.of("contract") == 2 && c.of("mask") == 2 && c.of("reduce") == 1
+                        : c.of("contract") == 3 && c.of("mask") == 0 && c.of("reduce") == 0,
+                 "dQ summary is not Q.K^T, dO.V^T and the gradient product");
+    for (const Operation &op : operations) {
+      if (op.name == "unary" && op.kind == "exp2") require(op.approximate && op.flush_to_zero, "exp2 must be approximate with flush_to_zero");
+      if (op.name == "compare") require(op.kind == (key_value ? "le" : "ge"), "causal mask must be key <= query");
+    }
+    const size_t outputs = key_value ? 2 : 1;
+    require(p.size() == 7 + outputs && p.back().kind == Parameter::kScalar && p.back().dtype == "f32",
+            "attention gradients take q, k, v, grad_output, lse, delta, outputs, scale");
+    const std::string dtype = p[0].dtype;
+    require(dtype == "f16" || dtype == "bf16", "attention gradient element type must be f16 or bf16");
+    require(view_is(p[0], 4, 0, dtype) && view_is(p[1], 4, 0, dtype) && view_is(p[2], 4, 0, dtype) && view_is(p[3], 4, 0, dtype) &&
+                view_is(p[4], 3, 0, "f32") && view_is(p[5], 3, 0, "f32") && view_is(p[6], 4, 1, dtype) &&
+                (!key_value || view_is(p[7], 4, 1, dtype)),
+            "attention gradient views must be four rank-4 inputs, lse and delta rank-3 f32, rank-4 outputs");
+    long long head_group = -1;
+    for (const Operation &op : operations) {
+      if (key_value) {
+        // group_query_count = HEAD_GROUP * Q: the first index product whose left operand is a constant
+        if (head_group < 0 && op.name == "binary" && op.kind == "multiply" && op.operands.size() == 2)
+          for (const Operation &other : operations)
+            if (other.name == "constant" && other.result == op.operands[0]) head_group = integer_constant(operations, op.operands[0]);
+      } else if (op.name == "binary" && op.kind == "floor_divide") {
+        require(op.operands.size() == 2, "floor_divide arity");
+        head_group = integer_constant(operations, op.operands[1]);
+      }
+    }
+    require(head_group >= 1, "HEAD_GROUP must be a positive constant");
+    plan.family = key_value ? "attention_backward_dkdv" : "attention_backward_dq";
+    plan.entry = key_value ? "b200_attention_backward_dkdv" : "b200_attention_backward_dq";
+    plan.tail = {{"dtype", dtype_code(dtype)}, {"head_group", head_group}, {"causal", causal}};
+    plan.workspace = true;
+    plan.alignment = 16;
+    return plan;
+  }
   if (c.of("region_fold") == 1) {
     // ---- flash attention: region_fold with Q.K^T and P.V contractions --------
     require(c.of("contract") == 2 && c.of("parallel") == 2 && c.of("transpose") == 1 && c.of("reduce") == 3 &&
@@ -405,6 +452,21 @@ Plan classify(const std::vector<Parameter> &all, const std::vector<Operation> &o
       plan.entry = "b200_csr_spmm";
     }
     plan.contiguous = {0, 1, 2};
+    return plan;
+  }
+  if (!heavy && c.of("parallel") == 2 && c.of("reduce") == 1 && c.of("view_load") == 2 && c.of("view_store") == 1) {
+    // ---- attention backward delta: row sums of f32(output) * f32(grad_output) -----------------
+    require(c.of("cast") == 2 && c.of("unary") == 0 && c.of("binary") == 2 && c.of("binary<multiply>") == 1 &&
+                c.of("binary<add>") == 1,
+            "two-level row reduction is not sum(output * grad_output)");
+    require(p.size() == 3, "attention_backward_delta takes output, grad_output, delta");
+    const std::string dtype = p[0].dtype;
+    require((dtype == "f16" || dtype == "bf16") && view_is(p[0], 4, 0, dtype) && view_is(p[1], 4, 0, dtype) &&
+                view_is(p[2], 3, 1, "f32"),
+            "attention_backward_delta views must be two rank-4 16-bit inputs and a rank-3 f32 output");
+    plan.family = "attention_backward_delta";
+    plan.entry = "b200_attention_backward_delta";
+    plan.tail = {{"dtype", dtype_code(dtype)}};
     return plan;
   }
   if (!heavy && c.of("scatter_reduce") == 2) {

@@ -60,9 +60,10 @@ def attention_inputs(b: int = 8, h: int = 32, s: int = 4096, d: int = 128, seed:
 
 
 def attention_backward_inputs(b: int = 2, hq: int = 8, hk: int = 2, s: int = 1024, d: int = 64, seed: int = 0,
-                              dtype=torch.float16, causal: bool = True, keys: int | None = None):
-    """q, k, v, output, grad_output, lse (natural log), scale for the backward trio; the forward
-    pass that yields output and lse is evaluated in f64 on the rounded operands.  Defaults are the
+                              dtype=torch.float16, causal: bool = True, keys: int | None = None, device=None):
+    """q, k, v, output, grad_output, lse (natural log), scale for the backward trio.  The forward
+    pass that yields output and lse is evaluated head by head on the rounded operands, in f64 on the
+    host, or in f32 on ``device`` when one is given (the large benchmark shape).  Defaults are the
     reference kernels' shape (kernels/backward/attention.py:7-13)."""
     rng = np.random.default_rng(seed)
     sk = s if keys is None else keys
@@ -72,13 +73,28 @@ def attention_backward_inputs(b: int = 2, hq: int = 8, hk: int = 2, s: int = 102
     grad_output = _f32(0.5 * rng.standard_normal((b, hq, s, d), dtype=np.float32)).to(dtype)
     scale = float(np.float32(1.0 / math.sqrt(d)))
     group = hq // hk
-    scores = torch.einsum("bhqd,bhkd->bhqk", q.double(), k.double().repeat_interleave(group, dim=1)) * scale
-    if causal:
-        allowed = torch.arange(sk)[None, :] <= torch.arange(s)[:, None]
-        scores = scores.masked_fill(~allowed, float("-inf"))
-    lse = torch.logsumexp(scores, dim=-1)
-    output = torch.einsum("bhqk,bhkd->bhqd", torch.exp(scores - lse[..., None]), v.double().repeat_interleave(group, dim=1))
-    return q, k, v, output.to(dtype), grad_output, lse.float(), scale
+    wide = torch.float64 if device is None else torch.float32
+    where = torch.device("cpu") if device is None else torch.device(device)
+    allowed = (torch.arange(sk, device=where)[None, :] <= torch.arange(s, device=where)[:, None]) if causal else None
+    output = torch.empty((b, hq, s, d), dtype=dtype)
+    lse = torch.empty((b, hq, s), dtype=torch.float32)
+    for batch in range(b):
+        for head in range(hq):
+            scores = (q[batch, head].to(where, wide) @ k[batch, head // group].to(where, wide).T) * scale
+            if causal:
+                scores = scores.masked_fill(~allowed, float("-inf"))
+            row_lse = torch.logsumexp(scores, dim=-1)
+            output[batch, head] = (torch.exp(scores - row_lse[:, None]) @ v[batch, head // group].to(where, wide)).to(dtype).cpu()
+            lse[batch, head] = row_lse.float().cpu()
+    return q, k, v, output, grad_output, lse, scale
+
+
+def attention_backward_workload(b=8, hq=32, hk=8, s=2048, d=128) -> Workload:
+    """delta + dK/dV + dQ: seven S x S x D products per query head over the causal half
+    (K.Q^T, V.dO^T, P^T.dO, dS^T.Q; Q.K^T, dO.V^T, dS.K)."""
+    flops = 7.0 * 2.0 * b * hq * (s * (s + 1) / 2) * d
+    return Workload("attention_backward", "TFLOP/s", "tensor", flops,
+                    f"causal attention backward f16 B={b} HQ={hq} HK={hk} S={s} D={d} (delta, dK/dV, dQ)")
 
 
 def csr_inputs(rows: int = 262144, columns: int = 262144, per_row: int = 32, features: int = 128,

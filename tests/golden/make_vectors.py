@@ -28,5 +28,11 @@ vectors["layer_norm_backward_dw_partial"], vectors["layer_norm_backward_db_parti
 vectors["layer_norm_backward_dw"], vectors["layer_norm_backward_db"] = oracle.layer_norm_backward_reduce(dw_partial, db_partial)
 p, u = workloads.softmax_backward_inputs(4, 20, seed=106)
 vectors["softmax_backward"] = oracle.softmax_backward(p, u)
+q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 2, 1, 24, 64, seed=107)
+delta = oracle.attention_backward_delta(output, grad_output)
+vectors["attention_backward_delta"] = delta
+vectors["attention_backward_grad_k"], vectors["attention_backward_grad_v"] = oracle.attention_backward_dkdv(
+    q, k, v, grad_output, lse, delta, scale, head_group=2)
+vectors["attention_backward_grad_q"] = oracle.attention_backward_dq(q, k, v, grad_output, lse, delta, scale, head_group=2)
 torch.save(vectors, Path(__file__).resolve().parent / "oracle_vectors.pt")
 print({k: tuple(v.shape) for k, v in vectors.items()})

@@ -28,6 +28,11 @@ EXPECTED = {
     "csr_spmv": ("csr_spmv", {}),
     "softmax_backward": ("softmax_backward", {"dtype": 0}),
     "layer_norm_backward_rows": ("layer_norm_backward_rows", {}),
+    "attention_backward_delta": ("attention_backward_delta", {"dtype": 1}),
+    "attention_backward_dkdv": ("attention_backward_dkdv", {"dtype": 1, "head_group": 4, "causal": 1}),
+    "attention_backward_dkdv_noncausal": ("attention_backward_dkdv", {"dtype": 1, "head_group": 1, "causal": 0}),
+    "attention_backward_dq": ("attention_backward_dq", {"dtype": 1, "head_group": 4, "causal": 1}),
+    "attention_backward_dq_noncausal": ("attention_backward_dq", {"dtype": 1, "head_group": 1, "causal": 0}),
     "layer_norm_backward_reduce": ("layer_norm_backward_reduce", {}),
     "csr_spmm_262144": ("csr_spmm", {}),
 }
@@ -49,7 +54,7 @@ def test_classification_and_metadata(name):
     layout = NativeLayout.read(metadata)                         # the NativeABI flavour parses
     assert metadata["target"] == {"family": "b200_native", "capabilities": b200.B200_CAPABILITIES}
     assert metadata["compile_options"] == {"numerics": "source", "optimizations": {}, "optimization_remarks": False}
-    assert bool(layout.workspaces) == (family in {"gemm", "flash_attention"})
+    assert bool(layout.workspaces) == (family in {"gemm", "flash_attention", "attention_backward_dkdv", "attention_backward_dq"})
 
 
 def test_interface_of_softmax_keeps_author_constraints():

@@ -144,6 +144,35 @@ def test_layer_norm_backward_pair_through_the_artifact_api():
     assert torch.equal(dw.cpu(), expected_dw) and torch.equal(db.cpu(), expected_db)
 
 
+def test_attention_backward_program():
+    """The reference's three-kernel recipe (examples/programs/attention_backward.py:19-41): delta,
+    dK/dV and dQ bound once, run as one prepared sequence that yields dQ, dK, dV."""
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(2, 8, 2, 512, 64, seed=13)
+    options = {"HEAD_GROUP": 4, "CAUSAL": True}
+    delta_kernel = b200.jit(b200.kernels.attention_backward_delta)
+    dkdv_kernel = b200.jit(b200.kernels.attention_backward_dkdv, constexprs=options)
+    dq_kernel = b200.jit(b200.kernels.attention_backward_dq, constexprs=options)
+    device = [t.to(DEV) for t in (q, k, v, output, grad_output, lse)]
+    delta = delta_kernel.prepare(device[3], device[4])
+    common = (device[0], device[1], device[2], device[4], device[5], delta.result(), scale)
+    dkdv = dkdv_kernel.prepare(*common)
+    dq = dq_kernel.prepare(*common)
+    sequence = b200.PreparedSequence((delta, dkdv, dq), outputs=(dq.result(), *dkdv.result()))
+    sequence.compile()
+    sequence.launch()
+    torch.cuda.synchronize()
+    dkdv.check()
+    dq.check()
+    grad_q, grad_k, grad_v = sequence.result()
+    expected_delta = oracle.attention_backward_delta(output, grad_output)
+    expected_k, expected_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, expected_delta, scale, head_group=4)
+    expected_q = oracle.attention_backward_dq(q, k, v, grad_output, lse, expected_delta, scale, head_group=4)
+    assert relative_error(grad_q, expected_q) <= 1e-2
+    assert relative_error(grad_k, expected_k) <= 1e-2
+    assert relative_error(grad_v, expected_v) <= 1e-2
+    assert sequence.kernel_count == 3
+
+
 def test_prepared_sequence_and_explicit_stream():
     (x,) = workloads.softmax_inputs(4096, 4097, seed=8)
     xd = x.to(DEV)

@@ -259,6 +259,61 @@ def test_layer_norm_backward_layout_errors():
         ops.layer_norm_backward_rows(*cuda(x, dy, w, mean, rstd, dw_partial, db_partial[:2]), inv)
 
 
+@pytest.mark.parametrize("b,hq,hk,s,d,causal,dtype", [
+    (1, 2, 1, 128, 64, True, torch.float16),
+    (1, 4, 2, 256, 64, True, torch.float16),
+    (1, 2, 2, 200, 64, False, torch.float16),      # ragged last tile, no mask
+    (2, 8, 2, 1024, 64, True, torch.float16),      # the reference kernels' shape
+    (1, 2, 1, 300, 128, True, torch.bfloat16),
+    (1, 1, 1, 1, 64, True, torch.float16),
+])
+def test_attention_backward(b, hq, hk, s, d, causal, dtype):
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(b, hq, hk, s, d, seed=s + d,
+                                                                                   dtype=dtype, causal=causal)
+    group = hq // hk
+    delta = ops.attention_backward_delta(*cuda(output, grad_output))
+    expected_delta = oracle.attention_backward_delta(output, grad_output)
+    assert relative_error(delta, expected_delta) <= 1e-5
+    device = cuda(q, k, v, grad_output, lse)
+    grad_k, grad_v = ops.attention_backward_dkdv(*device, delta, scale, head_group=group, causal=causal)
+    grad_q = ops.attention_backward_dq(*device, delta, scale, head_group=group, causal=causal)
+    ops.workspace_status(DEV)
+    expected_k, expected_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, expected_delta, scale,
+                                                            head_group=group, causal=causal)
+    expected_q = oracle.attention_backward_dq(q, k, v, grad_output, lse, expected_delta, scale, head_group=group,
+                                              causal=causal)
+    assert relative_error(grad_q, expected_q) <= 1e-2
+    assert relative_error(grad_k, expected_k) <= 1e-2
+    assert relative_error(grad_v, expected_v) <= 1e-2
+
+
+def test_attention_backward_matches_autograd_of_the_forward_kernel():
+    """dQ, dK, dV of the forward kernel's own output: the trio is its vector-Jacobian product."""
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 4, 1, 384, 64, seed=41)
+    device = cuda(q, k, v, grad_output, lse)
+    ours = ops.flash_attention(*device[:3], scale, head_group=4, causal=True)
+    delta = ops.attention_backward_delta(ours, device[3])
+    grad_k, grad_v = ops.attention_backward_dkdv(*device, delta, scale, head_group=4)
+    grad_q = ops.attention_backward_dq(*device, delta, scale, head_group=4)
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qd, kd.repeat_interleave(4, dim=1)) * scale
+    scores = scores.masked_fill(~torch.ones(384, 384, dtype=torch.bool).tril(), float("-inf"))
+    torch.einsum("bhqk,bhkd->bhqd", torch.softmax(scores, -1), vd.repeat_interleave(4, dim=1)).backward(grad_output.double())
+    assert relative_error(grad_q, qd.grad) <= 1e-2
+    assert relative_error(grad_k, kd.grad) <= 1e-2
+    assert relative_error(grad_v, vd.grad) <= 1e-2
+
+
+def test_attention_backward_argument_errors():
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 2, 1, 64, 32, seed=2)
+    delta = ops.attention_backward_delta(*cuda(output, grad_output))          # any head dimension
+    with pytest.raises(NotImplementedError):                                   # gradients: head dim 64 or 128
+        ops.attention_backward_dq(*cuda(q, k, v, grad_output, lse), delta, scale, head_group=2)
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 2, 1, 64, 64, seed=2)
+    with pytest.raises(ValueError):                                            # HQ != HK * head_group
+        ops.attention_backward_dkdv(*cuda(q, k, v, grad_output, lse), delta, scale, head_group=1)
+
+
 COLUMN_BLOCK_SCRIPT = """
 import sys, torch
 sys.path.insert(0, %r)

@@ -130,6 +130,25 @@ def test_layer_norm_backward_against_autograd():
     assert not torch.equal(again_w, dw_partial)
 
 
+def test_attention_backward_against_autograd():
+    b, hq, hk, s, d = 1, 4, 2, 96, 64
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(b, hq, hk, s, d, seed=29)
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qd, kd.repeat_interleave(2, dim=1)) * scale
+    scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool).tril(), float("-inf"))
+    torch.einsum("bhqk,bhkd->bhqd", torch.softmax(scores, -1), vd.repeat_interleave(2, dim=1)).backward(grad_output.double())
+    delta = oracle.attention_backward_delta(output, grad_output)
+    assert relative_error(delta, (output.double() * grad_output.double()).sum(-1)) <= 1e-5
+    grad_k, grad_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale, head_group=2)
+    grad_q = oracle.attention_backward_dq(q, k, v, grad_output, lse, delta, scale, head_group=2)
+    assert relative_error(grad_q, qd.grad) <= 1e-2
+    assert relative_error(grad_k, kd.grad) <= 1e-2
+    assert relative_error(grad_v, vd.grad) <= 1e-2
+    # the team size does not change the result (units are independent)
+    again_k, again_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale, head_group=2, workers=3)
+    assert torch.equal(again_k, grad_k) and torch.equal(again_v, grad_v)
+
+
 def test_committed_vectors():
     vectors = torch.load(GOLDEN)
     (x,) = workloads.softmax_inputs(4, 16, seed=100)
@@ -151,3 +170,10 @@ def test_committed_vectors():
     assert torch.equal(dw, vectors["layer_norm_backward_dw"]) and torch.equal(db, vectors["layer_norm_backward_db"])
     p, u = workloads.softmax_backward_inputs(4, 20, seed=106)
     assert torch.equal(oracle.softmax_backward(p, u), vectors["softmax_backward"])
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 2, 1, 24, 64, seed=107)
+    delta = oracle.attention_backward_delta(output, grad_output)
+    assert torch.equal(delta, vectors["attention_backward_delta"])
+    grad_k, grad_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale, head_group=2)
+    assert torch.equal(grad_k, vectors["attention_backward_grad_k"]) and torch.equal(grad_v, vectors["attention_backward_grad_v"])
+    assert torch.equal(oracle.attention_backward_dq(q, k, v, grad_output, lse, delta, scale, head_group=2),
+                       vectors["attention_backward_grad_q"])
