@@ -154,6 +154,57 @@ softmax_backward_kernel(const float *__restrict__ probabilities, const float *__
   }
 }
 
+// The same operator for rows of up to 8 * 1024 columns whose three matrices share one alignment
+// row by row: each row is peeled to its first 16-byte boundary (0..3 leading and 0..3 trailing
+// scalars, one per thread) and the body moves as 128-bit vectors that stay in registers between the
+// reduction and the write, so nothing is staged in shared memory.
+template <int VECTORS>
+__global__ void __launch_bounds__(256)
+softmax_backward_vector_kernel(const float *__restrict__ probabilities, const float *__restrict__ upstream,
+                               float *__restrict__ gradient, int64_t rows, int columns, int64_t p_pitch,
+                               int64_t u_pitch, int64_t g_pitch) {
+  __shared__ float scratch[2][8];
+  const int warp = threadIdx.x >> 5;
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float *p = probabilities + row * p_pitch, *u = upstream + row * u_pitch;
+    float *g = gradient + row * g_pitch;
+    const int lead = min(columns, (int)(((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) >> 2));
+    const int vectors = (columns - lead) >> 2, tail = columns - lead - 4 * vectors;
+    const float4 *p4 = reinterpret_cast<const float4 *>(p + lead), *u4 = reinterpret_cast<const float4 *>(u + lead);
+    float4 pv[VECTORS], uv[VECTORS];
+#pragma unroll
+    for (int v = 0; v < VECTORS; ++v) {
+      const int index = threadIdx.x + v * 256;
+      pv[v] = uv[v] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (index < vectors) { pv[v] = __ldcs(p4 + index); uv[v] = __ldcs(u4 + index); }
+    }
+    // the peeled scalars: thread e takes leading element e, or trailing element e - lead
+    const int edge = (int)threadIdx.x < lead ? (int)threadIdx.x
+                   : (int)threadIdx.x < lead + tail ? lead + 4 * vectors + ((int)threadIdx.x - lead) : -1;
+    float pe = 0.0f, ue = 0.0f;
+    if (edge >= 0) { pe = p[edge]; ue = u[edge]; }
+    float partial = __fmul_rn(pe, ue);
+#pragma unroll
+    for (int v = 0; v < VECTORS; ++v)
+      partial += __fmul_rn(pv[v].x, uv[v].x) + __fmul_rn(pv[v].y, uv[v].y) + __fmul_rn(pv[v].z, uv[v].z) +
+                 __fmul_rn(pv[v].w, uv[v].w);
+    const float projection = group_reduce<8, false>(partial, scratch[parity], warp, 1);
+    parity ^= 1;   // the next row's partial sums go to the other slot: one barrier per row is enough
+    float4 *g4 = reinterpret_cast<float4 *>(g + lead);
+#pragma unroll
+    for (int v = 0; v < VECTORS; ++v) {
+      const int index = threadIdx.x + v * 256;
+      if (index < vectors)
+        __stcs(g4 + index, make_float4(__fmul_rn(pv[v].x, __fsub_rn(uv[v].x, projection)),
+                                       __fmul_rn(pv[v].y, __fsub_rn(uv[v].y, projection)),
+                                       __fmul_rn(pv[v].z, __fsub_rn(uv[v].z, projection)),
+                                       __fmul_rn(pv[v].w, __fsub_rn(uv[v].w, projection))));
+    }
+    if (edge >= 0) g[edge] = __fmul_rn(pe, __fsub_rn(ue, projection));
+  }
+}
+
 // --------------------------------------------------------------- layer norm
 template <typename T, int WARPS, int ITERS, bool CENTERED>
 __global__ void __launch_bounds__(GroupShape<WARPS>::kCtaThreads)
@@ -504,6 +555,26 @@ extern "C" int b200_softmax_backward(const void *p, int64_t p_d0, int64_t p_d1, 
   if (p_d1 > 1 && (p_s1 != 1 || u_s1 != 1 || g_s1 != 1))
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "softmax_backward: inner strides must be 1");
   if (p_d1 > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "softmax_backward: row too long");
+  cudaStream_t queue = static_cast<cudaStream_t>(stream);
+  const uintptr_t pa = reinterpret_cast<uintptr_t>(p), ua = reinterpret_cast<uintptr_t>(dy), ga = reinterpret_cast<uintptr_t>(dx);
+  const bool same_alignment = (pa & 3) == 0 && (pa & 15) == (ua & 15) && (pa & 15) == (ga & 15) &&
+                              (p_s0 - u_s0) % 4 == 0 && (p_s0 - g_s0) % 4 == 0;
+  if (same_alignment && p_d1 <= 8 * 1024) {
+    const int per_thread = (int)((p_d1 / 4 + 255) / 256);
+    auto launch = [&](auto kernel) {
+      int resident = 0;   // not resident_ctas(): the four instantiations share one function type, hence one cache
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, 0) != cudaSuccess || resident < 1) resident = 1;
+      const int64_t limit = (int64_t)sm_count() * resident;
+      kernel<<<(unsigned)(p_d0 < limit ? p_d0 : limit), 256, 0, queue>>>((const float *)p, (const float *)dy, (float *)dx,
+                                                                        p_d0, (int)p_d1, p_s0, u_s0, g_s0);
+    };
+    if (per_thread <= 1) launch(softmax_backward_vector_kernel<1>);
+    else if (per_thread <= 2) launch(softmax_backward_vector_kernel<2>);
+    else if (per_thread <= 4) launch(softmax_backward_vector_kernel<4>);
+    else launch(softmax_backward_vector_kernel<8>);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  }
   const size_t row_bytes = 2 * (size_t)p_d1 * sizeof(float);
   const int staged = row_bytes <= 96 * 1024;
   const size_t smem = staged ? row_bytes : 0;
