@@ -404,11 +404,13 @@ class LayerNormBackwardCase(Case):
         self.ops, self.workload = ops, self.workloads.layer_norm_backward_workload()
         *tensors, self.inverse = self.workloads.layer_norm_backward_inputs()
         self.host = tuple(tensors)
-        self.dev = [t.to(device) for t in self.host]
-        self.dx = torch.empty_like(self.dev[0])
+        # 101 MB per step would fit L2: rotate over three copies of the matrices (302 MB) so DRAM is measured
+        self.sets = [[t.to(device) + 0 for t in self.host] + [torch.empty(4096, 4096, dtype=torch.bfloat16, device=device)]
+                     for _ in range(3)]
+        self.dev = self.sets[0][:7]
         self.dw = torch.empty(4096, device=device)
         self.db = torch.empty(4096, device=device)
-        self.flush = "three 33.5 MB matrices per launch; L2 flushed between timed steps is not needed: x, dy are streamed with evict-first loads and 101 MB of distinct lines move per step"
+        self.flush = "rotating three copies of the operands (302 MB > L2)"
         self.rows = b200.jit(b200.kernels.layer_norm_backward_rows)
         self.reduce = b200.jit(b200.kernels.layer_norm_backward_reduce)
         self.host_in = [pinned(t) for t in self.host]
@@ -421,8 +423,9 @@ class LayerNormBackwardCase(Case):
         self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
 
     def launch(self, step):
-        self.ops.layer_norm_backward_rows(*self.dev, self.inverse, out=self.dx)
-        self.ops.layer_norm_backward_reduce(self.dev[5], self.dev[6], dw=self.dw, db=self.db)
+        *operands, dx = self.sets[step % len(self.sets)]
+        self.ops.layer_norm_backward_rows(*operands, self.inverse, out=dx)
+        self.ops.layer_norm_backward_reduce(operands[5], operands[6], dw=self.dw, db=self.db)
 
     def e2e(self, step):
         for dev, host in zip(self.dev_in, self.host_in):

@@ -98,7 +98,9 @@ int b200_softmax_backward(const void *probabilities, int64_t p_d0, int64_t p_d1,
  * and the scatter-reductions dw_partial[row % G] += bf16(dy * xhat),
  * db_partial[row % G] += dy, G = dw_d0.  The reference promises no order for
  * colliding updates (doc/dsl/types-numerics-and-effects.en.md:242); this entry
- * applies the rows of a group in ascending order, each update rounded to bf16,
+ * fixes one: a group's rows are dealt round-robin to 8 lanes, each lane folds its
+ * rows in ascending order, the lane sums are combined in a fixed binary tree and
+ * the total is added to the previous contents, every add rounded to bf16,
  * so results do not vary from run to run.  dw_partial / db_partial are InOut:
  * their contents are accumulated into.  Unit inner strides; N a multiple of 8
  * and at most 8192; x, dy, dx, the partial rows and weight 16-byte aligned

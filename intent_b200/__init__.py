@@ -1,8 +1,10 @@
 """intent_b200 — a B200-native (sm_100a) provider for IntentDSL's operator hot path.
 
 Five operator families — row softmax, LayerNorm, dense GEMM, causal
-flash-attention, CSR SpMM — run as hand-written CUDA kernels behind a C ABI
-(``include/intent_b200.h``).  Two front doors reach them:
+flash-attention, CSR SpMM — and the kernels that pair with them (CSR SpMV, softmax
+backward, the LayerNorm backward pair, the attention backward trio) run as
+hand-written CUDA kernels behind a C ABI (``include/intent_b200.h``).  Two front
+doors reach them:
 
 * with the reference installed: ``intent_b200.register()`` then
   ``intent.jit(kernel, backend="b200", compiler=intent_b200.COMPILER)``;
@@ -10,6 +12,7 @@ flash-attention, CSR SpMM — run as hand-written CUDA kernels behind a C ABI
 
 Both run the same compile step (``b200-compile``), the same binder
 (``intent_b200.runtime``) and the same kernels; there is no other execution path.
+``python -m intent_b200 describe|doctor`` reports the interface and the environment.
 """
 from __future__ import annotations
 

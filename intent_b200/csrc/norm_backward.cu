@@ -1,178 +1,184 @@
-// LayerNorm backward (bf16 operands, f32 arithmetic): the row kernel's two halves and the
-// reduction of its partial sums.
+// LayerNorm backward (bf16 operands, f32 arithmetic): the row kernel and the reduction of its
+// partial sums.
 //
-// The reference's row kernel does two things per row: dx, which needs two sums over the row,
-// and the scatter-reduction of dy*xhat and dy into partial-sum row `row % G`, which needs no
-// row sum (xhat only takes the mean and rstd operands) but collides across rows.  They are
-// two launches here:
-//
-//   dx kernel        row-parallel: a group of 1..8 warps owns a row (up to 4 vectors of 8 bf16 per
-//                    thread, weight kept in registers), one named-barrier reduction of the pair
-//                    (sum w*dy, sum w*dy*xhat), dx written with streaming stores.  x and dy are
-//                    read with the default policy so that they stay in L2 for
-//   partials kernel  column-parallel: a thread owns 8 columns of one partial-sum row and walks that
-//                    group's rows g, g+G, ... in ascending order with loads four rows ahead, every
-//                    update rounded to bf16 (the typed combine): a fixed order, so the same result
-//                    on every run, and no atomics.
-//
-// Algorithmic bytes: 3*M*N*2 (x, dy, dx) + 4*G*N*2 (partials read and written) + N*2 + M*8;
-// the second read of x and dy is not counted (67 MB at the reference shape, mostly from L2).
+// Row kernel.  The scatter-reduction into partial-sum row `row % G` collides across the rows of a
+// group; the reference promises no order for colliding updates, so this file fixes one that maps
+// onto a thread-block cluster (every add is the typed bf16 add):
+//   the group's rows g, g+G, g+2G, ... are dealt round-robin to 8 lanes; each lane folds its rows
+//   in ascending order from zero; the lane sums are combined as ((s0+s1)+(s2+s3))+((s4+s5)+(s6+s7));
+//   the total is added to the element's previous contents.
+// A cluster of 8 CTAs owns one group and CTA l is lane l.  A CTA (8 warps) walks its lane's rows:
+// a thread owns 1, 2 or 4 vectors of 8 columns (N <= 2048, 4096, 8192), keeps the weight vector and its lane
+// sums in registers, requests the next row before it reduces the current one, forms the two row
+// sums (one barrier, double-buffered scratch) and writes dx with streaming stores.  The lane sums
+// then go to shared memory; after a cluster barrier CTA l reads the eight lanes' sums of its
+// eighth of the columns through distributed shared memory, combines them in the fixed tree, and
+// updates the partial-sum rows.  x and dy are read once, dx written once: no atomics, no scratch in
+// global memory, and the same result on every run.
+// Algorithmic bytes: 3*M*N*2 (x, dy, dx) + 4*G*N*2 (partials read and written) + N*2 + M*8.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int kVec = 8;          // bf16 per 128-bit access
-constexpr int kMaxVectors = 4;   // vectors per thread in the dx kernel
-constexpr int kDxThreads = 256;
-constexpr int kPrefetch = 4;     // rows in flight per thread in the partials kernel
+namespace cg = cooperative_groups;
 
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+constexpr int kVec = 8;             // bf16 per 128-bit access
+constexpr int kLanes = 8;           // CTAs per cluster = lanes of the update order
 
-template <int WARPS>
-__global__ void __launch_bounds__(kDxThreads)
-layer_norm_backward_dx_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ dy,
-                              const __nv_bfloat16 *__restrict__ weight, const float *__restrict__ mean,
-                              const float *__restrict__ rstd, __nv_bfloat16 *__restrict__ dx, int64_t rows,
-                              int columns, int64_t x_pitch, int64_t dy_pitch, int64_t dx_pitch,
-                              int64_t mean_stride, int64_t rstd_stride, float inverse_features) {
-  constexpr int kGroups = kDxThreads / 32 / WARPS;   // rows a CTA works on at once
-  __shared__ float scratch[2][kGroups][2][WARPS];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = warp / WARPS, warp_in_group = warp % WARPS;
-  const int first = (warp_in_group * 32 + lane) * kVec;        // vector v: + v * WARPS * 32 * kVec
-  constexpr int kStride = WARPS * 32 * kVec;
+// The typed combine, two elements at a time.  A packed bf16 add rounds the exact sum once; that is
+// the value bf16(f32(a) + f32(b)) of the definition: the f32 sum of two bf16 numbers is exact unless
+// their exponents lie more than 16 apart, and then both roundings return the larger operand.
+__device__ __forceinline__ __nv_bfloat162 combine(__nv_bfloat162 a, __nv_bfloat162 b) { return __hadd2(a, b); }
+__device__ __forceinline__ float low_of(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float high_of(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
 
-  float w[kMaxVectors][kVec];
+template <int kRowThreads, int VECTORS>
+__global__ void __cluster_dims__(kLanes, 1, 1) __launch_bounds__(kRowThreads, VECTORS > 2 ? 1 : 2)
+layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ dy,
+                                const __nv_bfloat16 *__restrict__ weight, const float *__restrict__ mean,
+                                const float *__restrict__ rstd, __nv_bfloat16 *__restrict__ dx,
+                                __nv_bfloat16 *__restrict__ dw_partial, __nv_bfloat16 *__restrict__ db_partial,
+                                int64_t rows, int columns, int groups, int64_t x_pitch, int64_t dy_pitch,
+                                int64_t dx_pitch, int64_t dw_pitch, int64_t db_pitch, int64_t mean_stride,
+                                int64_t rstd_stride, float inverse_features) {
+  constexpr int kRowStride = kRowThreads * kVec;   // columns between a thread's vectors
+  extern __shared__ __align__(16) __nv_bfloat16 lane_sums[];  // [dw | db][columns]
+  __shared__ float scratch[2][kRowThreads / 32][2];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int lane = (int)cluster.block_rank();
+  const int group = blockIdx.x / kLanes;
+  const int warp = threadIdx.x >> 5, thread_lane = threadIdx.x & 31;
+  const int first = threadIdx.x * kVec;
+
+  uint4 w[VECTORS];                                               // the weight vector, packed as loaded
+  __nv_bfloat162 dw[VECTORS][kVec / 2], db[VECTORS][kVec / 2];   // this lane's sums, packed
 #pragma unroll
-  for (int v = 0; v < kMaxVectors; ++v) {
+  for (int v = 0; v < VECTORS; ++v) {
+    w[v] = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int i = 0; i < kVec; ++i) w[v][i] = 0.0f;
-    if (first + v * kStride < columns) load_vector(weight + first + v * kStride, w[v]);
+    for (int i = 0; i < kVec / 2; ++i) dw[v][i] = db[v][i] = __floats2bfloat162_rn(0.0f, 0.0f);
+    if (first + v * kRowStride < columns) w[v] = *reinterpret_cast<const uint4 *>(weight + first + v * kRowStride);
   }
-  int parity = 0;
-  for (int64_t row = (int64_t)blockIdx.x * kGroups + group; row < rows; row += (int64_t)gridDim.x * kGroups) {
-    const float row_mean = mean[row * mean_stride], row_rstd = rstd[row * rstd_stride];
-    uint4 x_raw[kMaxVectors], dy_raw[kMaxVectors];
+  // rows of this group: group + j * groups for j < count; this CTA takes j = lane, lane + 8, ...
+  const int64_t count = rows > group ? (rows - group + groups - 1) / groups : 0;
+  const int64_t mine = count > lane ? (count - lane + kLanes - 1) / kLanes : 0;
+  uint4 x_next[VECTORS], dy_next[VECTORS];
+  float mean_next = 0.0f, rstd_next = 0.0f;
+  auto request = [&](int64_t step) {
+    const int64_t row = group + (lane + step * kLanes) * (int64_t)groups;
 #pragma unroll
-    for (int v = 0; v < kMaxVectors; ++v) {
-      x_raw[v] = dy_raw[v] = make_uint4(0, 0, 0, 0);
-      if (first + v * kStride < columns) {
-        x_raw[v] = *reinterpret_cast<const uint4 *>(x + row * x_pitch + first + v * kStride);
-        dy_raw[v] = *reinterpret_cast<const uint4 *>(dy + row * dy_pitch + first + v * kStride);
+    for (int v = 0; v < VECTORS; ++v) {
+      x_next[v] = dy_next[v] = make_uint4(0, 0, 0, 0);
+      if (step < mine && first + v * kRowStride < columns) {
+        x_next[v] = __ldcs(reinterpret_cast<const uint4 *>(x + row * x_pitch + first + v * kRowStride));
+        dy_next[v] = __ldcs(reinterpret_cast<const uint4 *>(dy + row * dy_pitch + first + v * kRowStride));
       }
     }
+    if (step < mine) { mean_next = mean[row * mean_stride]; rstd_next = rstd[row * rstd_stride]; }
+  };
+  request(0);
+  for (int64_t step = 0; step < mine; ++step) {
+    const int64_t row = group + (lane + step * kLanes) * (int64_t)groups;
+    const float row_mean = mean_next, row_rstd = rstd_next;
+    uint4 x_raw[VECTORS], dy_raw[VECTORS];
+#pragma unroll
+    for (int v = 0; v < VECTORS; ++v) { x_raw[v] = x_next[v]; dy_raw[v] = dy_next[v]; }
+    request(step + 1);
     float sum = 0.0f, sum_normalized = 0.0f;
 #pragma unroll
-    for (int v = 0; v < kMaxVectors; ++v) {
-      const __nv_bfloat16 *x_lanes = reinterpret_cast<const __nv_bfloat16 *>(&x_raw[v]);
-      const __nv_bfloat16 *dy_lanes = reinterpret_cast<const __nv_bfloat16 *>(&dy_raw[v]);
+    for (int v = 0; v < VECTORS; ++v) {
+      const uint32_t *x_pairs = reinterpret_cast<const uint32_t *>(&x_raw[v]);
+      const uint32_t *dy_pairs = reinterpret_cast<const uint32_t *>(&dy_raw[v]);
+      const uint32_t *w_pairs = reinterpret_cast<const uint32_t *>(&w[v]);
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        const float normalized = __fmul_rn(__fsub_rn(__bfloat162float(x_lanes[i]), row_mean), row_rstd);
-        const float weighted_dy = __fmul_rn(w[v][i], __bfloat162float(dy_lanes[i]));
-        sum += weighted_dy;
-        sum_normalized += __fmul_rn(weighted_dy, normalized);
+      for (int i = 0; i < kVec / 2; ++i) {
+        // dy * xhat is formed unfused, in the reference's order, so the lane sums do not depend on contraction
+        const float d0 = low_of(dy_pairs[i]), d1 = high_of(dy_pairs[i]);
+        const float n0 = __fmul_rn(__fsub_rn(low_of(x_pairs[i]), row_mean), row_rstd);
+        const float n1 = __fmul_rn(__fsub_rn(high_of(x_pairs[i]), row_mean), row_rstd);
+        const float g0 = low_of(w_pairs[i]) * d0, g1 = high_of(w_pairs[i]) * d1;
+        sum += g0 + g1;
+        sum_normalized = fmaf(g0, n0, fmaf(g1, n1, sum_normalized));
+        dw[v][i] = combine(dw[v][i], __floats2bfloat162_rn(__fmul_rn(d0, n0), __fmul_rn(d1, n1)));
+        db[v][i] = combine(db[v][i], *reinterpret_cast<const __nv_bfloat162 *>(&dy_pairs[i]));
       }
     }
     sum = warp_sum(sum);
     sum_normalized = warp_sum(sum_normalized);
-    if (WARPS > 1) {
-      if (lane == 0) { scratch[parity][group][0][warp_in_group] = sum; scratch[parity][group][1][warp_in_group] = sum_normalized; }
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(WARPS * 32) : "memory");
-      sum = sum_normalized = 0.0f;
+    float (*slot)[2] = scratch[step & 1];
+    if (thread_lane == 0) { slot[warp][0] = sum; slot[warp][1] = sum_normalized; }
+    __syncthreads();   // the other parity's slots are free again once every thread is past this point
+    float total = 0.0f, total_normalized = 0.0f;
 #pragma unroll
-      for (int other = 0; other < WARPS; ++other) {
-        sum += scratch[parity][group][0][other];
-        sum_normalized += scratch[parity][group][1][other];
-      }
-      parity ^= 1;   // the other slot is free again once the group has passed the next barrier
-    }
-    const float mean_weighted_dy = sum * inverse_features;
-    const float mean_weighted_dy_normalized = sum_normalized * inverse_features;
+    for (int other = 0; other < kRowThreads / 32; ++other) { total += slot[other][0]; total_normalized += slot[other][1]; }
+    const float mean_weighted_dy = total * inverse_features;
+    const float mean_weighted_dy_normalized = total_normalized * inverse_features;
 #pragma unroll
-    for (int v = 0; v < kMaxVectors; ++v) {
-      if (first + v * kStride >= columns) continue;
-      const __nv_bfloat16 *x_lanes = reinterpret_cast<const __nv_bfloat16 *>(&x_raw[v]);
-      const __nv_bfloat16 *dy_lanes = reinterpret_cast<const __nv_bfloat16 *>(&dy_raw[v]);
+    for (int v = 0; v < VECTORS; ++v) {
+      if (first + v * kRowStride >= columns) continue;
+      const uint32_t *x_pairs = reinterpret_cast<const uint32_t *>(&x_raw[v]);
+      const uint32_t *dy_pairs = reinterpret_cast<const uint32_t *>(&dy_raw[v]);
+      const uint32_t *w_pairs = reinterpret_cast<const uint32_t *>(&w[v]);
       uint4 raw;
-      __nv_bfloat16 *lanes = reinterpret_cast<__nv_bfloat16 *>(&raw);
+      __nv_bfloat162 *pairs = reinterpret_cast<__nv_bfloat162 *>(&raw);
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        const float normalized = __fmul_rn(__fsub_rn(__bfloat162float(x_lanes[i]), row_mean), row_rstd);
-        const float weighted_dy = __fmul_rn(w[v][i], __bfloat162float(dy_lanes[i]));
-        lanes[i] = __float2bfloat16_rn((weighted_dy - mean_weighted_dy - normalized * mean_weighted_dy_normalized) * row_rstd);
+      for (int i = 0; i < kVec / 2; ++i) {
+        const float n0 = __fmul_rn(__fsub_rn(low_of(x_pairs[i]), row_mean), row_rstd);
+        const float n1 = __fmul_rn(__fsub_rn(high_of(x_pairs[i]), row_mean), row_rstd);
+        const float g0 = low_of(w_pairs[i]) * low_of(dy_pairs[i]), g1 = high_of(w_pairs[i]) * high_of(dy_pairs[i]);
+        pairs[i] = __floats2bfloat162_rn((g0 - mean_weighted_dy - n0 * mean_weighted_dy_normalized) * row_rstd,
+                                         (g1 - mean_weighted_dy - n1 * mean_weighted_dy_normalized) * row_rstd);
       }
-      __stcs(reinterpret_cast<uint4 *>(dx + row * dx_pitch + first + v * kStride), raw);
+      __stcs(reinterpret_cast<uint4 *>(dx + row * dx_pitch + first + v * kRowStride), raw);
     }
   }
+  // this lane's sums, for the whole cluster to read
+#pragma unroll
+  for (int v = 0; v < VECTORS; ++v) {
+    const int column = first + v * kRowStride;
+    if (column >= columns) continue;
+    *reinterpret_cast<uint4 *>(lane_sums + column) = *reinterpret_cast<const uint4 *>(dw[v]);
+    *reinterpret_cast<uint4 *>(lane_sums + columns + column) = *reinterpret_cast<const uint4 *>(db[v]);
+  }
+  cluster.sync();
+  // CTA `lane` combines its eighth of the columns (in vectors of 8)
+  const int vectors = columns / kVec, share = (vectors + kLanes - 1) / kLanes;
+  for (int index = lane * share + threadIdx.x; index < min(vectors, (lane + 1) * share); index += kRowThreads) {
+    const int column = index * kVec;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16 *destination = (which ? db_partial + group * db_pitch : dw_partial + group * dw_pitch) + column;
+      uint4 level[kLanes];
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l)
+        level[l] = *reinterpret_cast<const uint4 *>(cluster.map_shared_rank(lane_sums, l) + which * columns + column);
+#pragma unroll
+      for (int width = 1; width < kLanes; width <<= 1)
+#pragma unroll
+        for (int l = 0; l < kLanes; l += 2 * width) {
+          __nv_bfloat162 *into = reinterpret_cast<__nv_bfloat162 *>(&level[l]);
+          const __nv_bfloat162 *from = reinterpret_cast<const __nv_bfloat162 *>(&level[l + width]);
+#pragma unroll
+          for (int i = 0; i < kVec / 2; ++i) into[i] = combine(into[i], from[i]);
+        }
+      uint4 old = *reinterpret_cast<const uint4 *>(destination);
+      __nv_bfloat162 *result = reinterpret_cast<__nv_bfloat162 *>(&old);
+      const __nv_bfloat162 *total = reinterpret_cast<const __nv_bfloat162 *>(&level[0]);
+#pragma unroll
+      for (int i = 0; i < kVec / 2; ++i) result[i] = combine(result[i], total[i]);
+      *reinterpret_cast<uint4 *>(destination) = old;
+    }
+  }
+  cluster.sync();   // no CTA may leave while another still reads its shared memory
 }
 
-__global__ void __launch_bounds__(256)
-layer_norm_backward_partials_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ dy,
-                                    const float *__restrict__ mean, const float *__restrict__ rstd,
-                                    __nv_bfloat16 *__restrict__ dw_partial, __nv_bfloat16 *__restrict__ db_partial,
-                                    int64_t rows, int vectors, int groups, int64_t x_pitch, int64_t dy_pitch,
-                                    int64_t dw_pitch, int64_t db_pitch, int64_t mean_stride, int64_t rstd_stride) {
-  const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (index >= (int64_t)groups * vectors) return;
-  const int group = (int)(index / vectors), column = (int)(index % vectors) * kVec;
-  float dw[kVec], db[kVec];
-  load_vector(dw_partial + group * dw_pitch + column, dw);
-  load_vector(db_partial + group * db_pitch + column, db);
-
-  // rows of this group: group, group + groups, ...
-  const int64_t count = rows > group ? (rows - group + groups - 1) / groups : 0;
-  uint4 x_next[kPrefetch], dy_next[kPrefetch];
-  float mean_next[kPrefetch], rstd_next[kPrefetch];
-#pragma unroll
-  for (int stage = 0; stage < kPrefetch; ++stage) {
-    x_next[stage] = dy_next[stage] = make_uint4(0, 0, 0, 0);
-    mean_next[stage] = rstd_next[stage] = 0.0f;
-    if (stage < count) {
-      const int64_t row = group + (int64_t)stage * groups;
-      mean_next[stage] = mean[row * mean_stride];
-      rstd_next[stage] = rstd[row * rstd_stride];
-      x_next[stage] = *reinterpret_cast<const uint4 *>(x + row * x_pitch + column);
-      dy_next[stage] = *reinterpret_cast<const uint4 *>(dy + row * dy_pitch + column);
-    }
-  }
-  for (int64_t step = 0; step < count; ++step) {
-    const uint4 x_raw = x_next[0], dy_raw = dy_next[0];
-    const float row_mean = mean_next[0], row_rstd = rstd_next[0];
-#pragma unroll
-    for (int stage = 0; stage + 1 < kPrefetch; ++stage) {
-      x_next[stage] = x_next[stage + 1];
-      dy_next[stage] = dy_next[stage + 1];
-      mean_next[stage] = mean_next[stage + 1];
-      rstd_next[stage] = rstd_next[stage + 1];
-    }
-    if (step + kPrefetch < count) {
-      const int64_t ahead = group + (step + kPrefetch) * groups;
-      mean_next[kPrefetch - 1] = mean[ahead * mean_stride];
-      rstd_next[kPrefetch - 1] = rstd[ahead * rstd_stride];
-      x_next[kPrefetch - 1] = *reinterpret_cast<const uint4 *>(x + ahead * x_pitch + column);
-      dy_next[kPrefetch - 1] = *reinterpret_cast<const uint4 *>(dy + ahead * dy_pitch + column);
-    }
-    const __nv_bfloat16 *x_lanes = reinterpret_cast<const __nv_bfloat16 *>(&x_raw);
-    const __nv_bfloat16 *dy_lanes = reinterpret_cast<const __nv_bfloat16 *>(&dy_raw);
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) {
-      const float dy_value = __bfloat162float(dy_lanes[i]);
-      // unfused, in the reference's order: these values take no part in the row sums
-      const float normalized = __fmul_rn(__fsub_rn(__bfloat162float(x_lanes[i]), row_mean), row_rstd);
-      dw[i] = round_bf16(dw[i] + round_bf16(__fmul_rn(dy_value, normalized)));
-      db[i] = round_bf16(db[i] + dy_value);
-    }
-  }
-  store_vector(dw_partial + group * dw_pitch + column, dw);
-  store_vector(db_partial + group * db_pitch + column, db);
-}
-
-// dw[n] = sum over groups (ascending) of f32(dw_partial[g, n]); likewise db.  A CTA owns 32 columns:
+// dw[n] = sum over groups (ascending) of f32(dw_partial[g, n]); likewise db.  A CTA owns 16 columns:
 // all threads stage up to 128 group rows of both matrices in shared memory at once (so every load of
 // the tile is in flight together), then one thread per (matrix, column) adds them in group order.
-constexpr int kReduceColumns = 32, kReduceGroups = 128, kReduceThreads = 128;
+constexpr int kReduceColumns = 16, kReduceGroups = 128, kReduceThreads = 256;
 
 __global__ void __launch_bounds__(kReduceThreads)
 layer_norm_backward_reduce_kernel(const __nv_bfloat16 *__restrict__ dw_partial,
@@ -182,7 +188,7 @@ layer_norm_backward_reduce_kernel(const __nv_bfloat16 *__restrict__ dw_partial,
   constexpr int kPairs = kReduceColumns / 2;
   __shared__ __align__(16) __nv_bfloat16 tile[2][kReduceGroups][kReduceColumns];
   const int column0 = blockIdx.x * kReduceColumns;
-  const int which = threadIdx.x / kReduceColumns, mine = threadIdx.x % kReduceColumns;  // threads 0..63 add
+  const int which = threadIdx.x / kReduceColumns, mine = threadIdx.x % kReduceColumns;  // threads 0..31 add
   const int pair = threadIdx.x % kPairs, first_group = threadIdx.x / kPairs;            // staging role
   constexpr int kGroupStep = kReduceThreads / kPairs;
   const int column = column0 + 2 * pair;
@@ -194,7 +200,7 @@ layer_norm_backward_reduce_kernel(const __nv_bfloat16 *__restrict__ dw_partial,
     for (int matrix = 0; matrix < 2; ++matrix) {
       const __nv_bfloat16 *base = matrix ? db_partial : dw_partial;
       const int64_t pitch = matrix ? db_pitch : dw_pitch;
-#pragma unroll 8
+#pragma unroll 4
       for (int g = first_group; g < here; g += kGroupStep) {
         const __nv_bfloat16 *source = base + (group0 + g) * pitch + column;
         __nv_bfloat162 value = __floats2bfloat162_rn(0.0f, 0.0f);
@@ -247,29 +253,24 @@ extern "C" int b200_layer_norm_backward_rows(
   if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(dw_partial) || !aligned16(db_partial) ||
       !aligned16(weight) || x_s0 % kVec || dy_s0 % kVec || dx_s0 % kVec || dw_s0 % kVec || db_s0 % kVec)
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "layer_norm_backward_rows: rows must be 16-byte aligned");
-  if (dw_d0 > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "layer_norm_backward_rows: too many groups");
+  if (dw_d0 > INT32_MAX / kLanes) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "layer_norm_backward_rows: too many groups");
   cudaStream_t queue = static_cast<cudaStream_t>(stream);
-  const int vectors = (int)(n / kVec);
-  const int warps = vectors <= 128 ? 1 : vectors <= 256 ? 2 : vectors <= 512 ? 4 : 8;   // <= 4 vectors per thread
-  auto launch_dx = [&](auto kernel, int rows_per_cta) {
-    const int64_t wanted = (m + rows_per_cta - 1) / rows_per_cta;
-    const int64_t limit = (int64_t)sm_count() * 8;
-    kernel<<<(unsigned)(wanted < limit ? wanted : limit), kDxThreads, 0, queue>>>(
+  const size_t smem = 2 * (size_t)n * sizeof(__nv_bfloat16);
+  auto launch = [&](auto kernel, int threads) -> cudaError_t {
+    if (smem > 48 * 1024) {
+      const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (error != cudaSuccess) return error;
+    }
+    kernel<<<(unsigned)(dw_d0 * kLanes), threads, smem, queue>>>(
         (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)dy, (const __nv_bfloat16 *)weight, (const float *)mean,
-        (const float *)rstd, (__nv_bfloat16 *)dx, m, (int)n, x_s0, dy_s0, dx_s0, mean_s0, rstd_s0, inverse_features);
+        (const float *)rstd, (__nv_bfloat16 *)dx, (__nv_bfloat16 *)dw_partial, (__nv_bfloat16 *)db_partial, m, (int)n,
+        (int)dw_d0, x_s0, dy_s0, dx_s0, dw_s0, db_s0, mean_s0, rstd_s0, inverse_features);
+    return cudaGetLastError();
   };
-  switch (warps) {
-  case 1: launch_dx(layer_norm_backward_dx_kernel<1>, 8); break;
-  case 2: launch_dx(layer_norm_backward_dx_kernel<2>, 4); break;
-  case 4: launch_dx(layer_norm_backward_dx_kernel<4>, 2); break;
-  default: launch_dx(layer_norm_backward_dx_kernel<8>, 1); break;
-  }
-  B200_CUDA_TRY(cudaGetLastError());
-  const int64_t threads = dw_d0 * vectors;
-  layer_norm_backward_partials_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, queue>>>(
-      (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)dy, (const float *)mean, (const float *)rstd,
-      (__nv_bfloat16 *)dw_partial, (__nv_bfloat16 *)db_partial, m, vectors, (int)dw_d0, x_s0, dy_s0, dw_s0, db_s0,
-      mean_s0, rstd_s0);
+  // 8 warps per row; 1, 2 or 4 vectors of 8 columns per thread
+  if (n <= 256 * kVec) B200_CUDA_TRY(launch(layer_norm_backward_rows_kernel<256, 1>, 256));
+  else if (n <= 512 * kVec) B200_CUDA_TRY(launch(layer_norm_backward_rows_kernel<256, 2>, 256));
+  else B200_CUDA_TRY(launch(layer_norm_backward_rows_kernel<256, 4>, 256));
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

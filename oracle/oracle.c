@@ -600,20 +600,30 @@ int oracle_softmax_backward(const float *p, const float *u, float *g, int64_t m,
 
 /* layer_norm_backward_rows  kernels/backward/layer_norm.py:12-66 (bf16 operands, f32 arithmetic).
    scatter_reduce combines repeated addresses with the typed bf16 add and promises no order
-   (doc/dsl/types-numerics-and-effects.en.md:242); this restatement fixes one: the rows of a
-   group (row % groups) in ascending order, each update rounded to bf16.  Work is split over
-   groups so the order does not depend on the team size. */
+   (doc/dsl/types-numerics-and-effects.en.md:242); this restatement fixes one.  For one element of
+   partial-sum row g the rows g, g+G, g+2G, ... are dealt round-robin to 8 lanes; each lane folds
+   its rows in ascending order from zero; the lane sums are combined as
+   ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)); the total is added to the element's previous contents.
+   Every add is rounded to bf16.  Work is split over groups, so the team size changes nothing. */
+#define SCATTER_LANES 8
 struct layer_norm_backward_args {
   const uint16_t *x, *dy, *weight; const float *mean, *rstd;
   uint16_t *dx, *dw_partial, *db_partial;
   int64_t m, n, groups, xs0, dys0, dxs0, dws0, dbs0;
   float inverse_features;
 };
+static inline float bf16_add(float a, float b) { return bf16_to_f32(f32_to_bf16(a + b)); }
 static void layer_norm_backward_groups(void *opaque, int64_t begin, int64_t end) {
   const struct layer_norm_backward_args *a = opaque;
+  float *lanes_w = malloc((size_t)SCATTER_LANES * a->n * sizeof(float));
+  float *lanes_b = malloc((size_t)SCATTER_LANES * a->n * sizeof(float));
+  if (!lanes_w || !lanes_b) { free(lanes_w); free(lanes_b); return; }
   for (int64_t g = begin; g < end; ++g) {
     uint16_t *dw = a->dw_partial + g * a->dws0, *db = a->db_partial + g * a->dbs0;
-    for (int64_t r = g; r < a->m; r += a->groups) {
+    for (int64_t i = 0; i < SCATTER_LANES * a->n; ++i) lanes_w[i] = lanes_b[i] = 0.0f;
+    int64_t j = 0;
+    for (int64_t r = g; r < a->m; r += a->groups, ++j) {
+      float *lane_w = lanes_w + (j % SCATTER_LANES) * a->n, *lane_b = lanes_b + (j % SCATTER_LANES) * a->n;
       const uint16_t *x = a->x + r * a->xs0, *dy = a->dy + r * a->dys0;
       uint16_t *dx = a->dx + r * a->dxs0;
       const float row_mean = a->mean[r], row_rstd = a->rstd[r];
@@ -633,11 +643,20 @@ static void layer_norm_backward_groups(void *opaque, int64_t begin, int64_t end)
         const float weighted_dy = bf16_to_f32(a->weight[c]) * dy_value;
         dx[c] = f32_to_bf16((weighted_dy - mean_weighted_dy - normalized * mean_weighted_dy_normalized) * row_rstd);
         const float dw_value = bf16_to_f32(f32_to_bf16(dy_value * normalized));
-        dw[c] = f32_to_bf16(bf16_to_f32(dw[c]) + dw_value);
-        db[c] = f32_to_bf16(bf16_to_f32(db[c]) + dy_value);
+        lane_w[c] = bf16_add(lane_w[c], dw_value);
+        lane_b[c] = bf16_add(lane_b[c], dy_value);
       }
     }
+    for (int64_t c = 0; c < a->n; ++c) {
+      float w[SCATTER_LANES], b[SCATTER_LANES];
+      for (int l = 0; l < SCATTER_LANES; ++l) { w[l] = lanes_w[l * a->n + c]; b[l] = lanes_b[l * a->n + c]; }
+      for (int width = 1; width < SCATTER_LANES; width *= 2)
+        for (int l = 0; l < SCATTER_LANES; l += 2 * width) { w[l] = bf16_add(w[l], w[l + width]); b[l] = bf16_add(b[l], b[l + width]); }
+      dw[c] = f32_to_bf16(bf16_to_f32(dw[c]) + w[0]);
+      db[c] = f32_to_bf16(bf16_to_f32(db[c]) + b[0]);
+    }
   }
+  free(lanes_w); free(lanes_b);
 }
 int oracle_layer_norm_backward_rows(const uint16_t *x, const uint16_t *dy, const uint16_t *weight, const float *mean,
                                     const float *rstd, uint16_t *dx, uint16_t *dw_partial, uint16_t *db_partial,

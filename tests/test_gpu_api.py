@@ -189,3 +189,11 @@ def test_prepared_sequence_and_explicit_stream():
     expected = oracle.softmax_backward(oracle.softmax(x[:32]), upstream[:32].cpu())
     assert relative_error(sequence.result()[:32], expected) <= 1e-4
     assert [o.stage for o in sequence.observations] == ["launched", "launched"]
+
+
+def test_doctor_resolves_the_device():
+    from intent_b200 import tools
+    report = tools.doctor(0)
+    assert report["status"] == "available", report
+    target = report["checks"][-1]
+    assert target["name"] == "target" and target["detail"]["capabilities"]["compute_capability_major"] == 10

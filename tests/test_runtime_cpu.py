@@ -79,3 +79,19 @@ def test_torch_op_schema_and_fake_kernel():
         w = torch.empty(32, dtype=torch.float16)
         out = op(x, w, w, 1 / 32, 1e-5)
         assert out.shape == (6, 32) and out.dtype == torch.float16
+
+
+def test_describe_and_doctor_views():
+    """The b200 views of the reference's `describe` and `doctor` tools
+    (python/intent/tools/compilation.py:125-153, 343-455): dictionaries, nothing compiled or run."""
+    from intent_b200 import tools
+    described = tools.describe()
+    assert described["status"] == "described" and described["tool_invoked_kernel"] is False
+    assert "b200_flash_attention" in described["entries"] and "attention_backward_dq" in described["kernels"]
+    assert described["backends"]["b200"]["local_device"] == {"kind": "cuda", "indexed": True}
+    report = tools.doctor(None)                       # compiler and library only: no device here
+    assert report["status"] == "available" and report["tool_invoked_kernel"] is False
+    assert [item["name"] for item in report["checks"]] == ["b200 compile step", "native library", "torch"]
+    missing = tools.doctor(None, compiler="/nonexistent/b200-compile")
+    assert missing["status"] == "unavailable" and missing["checks"][0]["status"] == "unavailable"
+    assert tools.main(["describe"]) == 0
