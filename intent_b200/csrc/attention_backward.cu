@@ -22,7 +22,8 @@
 //
 //   warp 0      TMA producer (X0, X1 once; Y0, Y1 through a ring)
 //   warp 1      MMA issuer (one elected thread)
-//   warps 2..5  compute: thread r owns TMEM lane r; 32 columns of T0 and T1 at a time
+//   warps 2..9  compute: two threads per TMEM lane, 64 columns of T0 and T1 each (32 at a time); a
+//               thread writes its packed P, G over the first 32 of its own 64 columns
 // Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag and reports
 // its site in the caller's workspace words.
 #include <mutex>
@@ -34,7 +35,7 @@ namespace b200 {
 namespace {
 
 constexpr int kTile = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;      // producer warp, MMA warp, 2 column halves x 4 compute warps
 constexpr int kTmemColumns = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -48,7 +49,7 @@ struct __align__(8) Barriers {
   uint64_t x_full, y_full[4], y_empty[4], t_full, g_ready, acc_full;
   uint32_t tmem_base;
   int abort_flag;
-  float columns[4][2][kTile];   // MODE 0: [compute warp][lse*log2e | delta][query column] of the current step
+  float columns[8][2][kTile / 2];   // MODE 0: [compute warp][lse*log2e | delta][its 64 query columns] of the current step
 };
 
 struct Shape {
@@ -88,7 +89,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
   Barriers *bars = reinterpret_cast<Barriers *>(ring + kStages * 2 * L::kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_index = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  // heaviest tiles first: the first key tile (MODE 0) and the last query tile (MODE 1) walk the most steps
+  const int tile_index = MODE == 1 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
   const int row0 = tile_index * kTile;                          // first key (MODE 0) / query (MODE 1) of the CTA
   const int streamed_extent = MODE == 0 ? shape.seq_q : shape.seq_k;
   const int streamed_tiles = (streamed_extent + kTile - 1) / kTile;
@@ -112,7 +115,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
       tc::mbar_init(&bars->y_empty[s], 1);
     }
     tc::mbar_init(&bars->t_full, 1);
-    tc::mbar_init(&bars->g_ready, 4);
+    tc::mbar_init(&bars->g_ready, 8);
     tc::mbar_init(&bars->acc_full, 1);
     bars->abort_flag = 0;
     tc::mbar_fence_init();
@@ -196,11 +199,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
         tc::tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          // A: 16 streamed rows = 8 packed TMEM columns; B: the same 16 rows of Y, 2048 bytes apart
-          tc::mma_f16_ts(tmem_acc1, tmem_t1 + kk * 8,
+          // B: the same 16 rows of Y, 2048 bytes apart
+          // key block kk (16 streamed rows, 8 packed columns) was written by column half kk/4 into its own columns
+          tc::mma_f16_ts(tmem_acc1, tmem_t1 + (kk / 4) * 64 + (kk % 4) * 8,
                          tc::smem_desc_mn_major_sw128(y_address + kk * 2048, L::kHalfBytes), idesc_acc, (step | kk) != 0);
           if (MODE == 0)
-            tc::mma_f16_ts(tmem_acc0, tmem_t0 + kk * 8,
+            tc::mma_f16_ts(tmem_acc0, tmem_t0 + (kk / 4) * 64 + (kk % 4) * 8,
                            tc::smem_desc_mn_major_sw128(y_address + L::kTileBytes + kk * 2048, L::kHalfBytes), idesc_acc,
                            (step | kk) != 0);
         }
@@ -211,6 +215,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
   } else {
     // -------------------------------------------------------------- compute
     const int quadrant = warp & 3;                       // TMEM lanes [32*quadrant, +32) are this warp's
+    const int half = (warp - 2) >> 2;                    // columns [64*half, +64) of the step are this thread's
+    const int compute_warp = warp - 2;
     const int row_in_tile = quadrant * 32 + lane;
     const int row = row0 + row_in_tile;                  // key (MODE 0) or query (MODE 1) index of this lane
     const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
@@ -231,15 +237,15 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
         // between warps is needed (the previous step's reads ended at its __syncwarp)
         const int hq = y_head(step);
 #pragma unroll
-        for (int part = 0; part < kTile / 32; ++part) {
-          const int query = streamed0 + part * 32 + lane;
+        for (int part = 0; part < kTile / 64; ++part) {
+          const int query = streamed0 + half * 64 + part * 32 + lane;
           float l = INFINITY, d = 0.0f;
           if (query < shape.seq_q) {
             l = lse[batch * shape.lse_stride[0] + hq * shape.lse_stride[1] + query * shape.lse_stride[2]] * kLog2e;
             d = delta[batch * shape.delta_stride[0] + hq * shape.delta_stride[1] + query * shape.delta_stride[2]];
           }
-          bars->columns[quadrant][0][part * 32 + lane] = l;
-          bars->columns[quadrant][1][part * 32 + lane] = d;
+          bars->columns[compute_warp][0][part * 32 + lane] = l;
+          bars->columns[compute_warp][1][part * 32 + lane] = d;
         }
         __syncwarp();
       }
@@ -251,10 +257,10 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
       const int diagonal = row - streamed0;
       const bool masked = shape.causal && (MODE == 0 ? streamed0 < row0 + kTile - 1 : streamed0 + kTile - 1 > row0);
 #pragma unroll 1
-      for (int chunk = 0; chunk < kTile / 32; ++chunk) {
+      for (int chunk = 0; chunk < kTile / 64; ++chunk) {
         uint32_t t0[32], t1[32];
-        tc::tmem_load_32x32(tmem_t0 + lane_base + chunk * 32, t0);
-        tc::tmem_load_32x32(tmem_t1 + lane_base + chunk * 32, t1);
+        tc::tmem_load_32x32(tmem_t0 + lane_base + half * 64 + chunk * 32, t0);
+        tc::tmem_load_32x32(tmem_t1 + lane_base + half * 64 + chunk * 32, t1);
         tc::tmem_load_wait();
         uint32_t p16[16], g16[16];
 #pragma unroll
@@ -262,9 +268,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
           float p[2], g[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int column = chunk * 32 + 2 * i + e;
-            const float l = MODE == 0 ? bars->columns[quadrant][0][column] : row_lse;
-            const float d = MODE == 0 ? bars->columns[quadrant][1][column] : row_delta;
+            const int mine = chunk * 32 + 2 * i + e, column = half * 64 + mine;
+            const float l = MODE == 0 ? bars->columns[compute_warp][0][mine] : row_lse;
+            const float d = MODE == 0 ? bars->columns[compute_warp][1][mine] : row_delta;
             float probability = ex2_approx_ftz(fmaf(__uint_as_float(t0[2 * i + e]), shape.score_scale, -l));
             if (masked && (MODE == 0 ? column < diagonal : column > diagonal)) probability = 0.0f;
             p[e] = probability;
@@ -273,9 +279,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
           p16[i] = pack_pair<T>(p[0], p[1]);
           g16[i] = pack_pair<T>(g[0], g[1]);
         }
-        // packed columns [16*chunk, +16) lie over f32 columns this thread has already consumed
-        if (MODE == 0) tc::tmem_store_32x16(tmem_t0 + lane_base + chunk * 16, p16);
-        tc::tmem_store_32x16(tmem_t1 + lane_base + chunk * 16, g16);
+        // packed columns [64*half + 16*chunk, +16) lie over f32 columns this thread has already consumed
+        if (MODE == 0) tc::tmem_store_32x16(tmem_t0 + lane_base + half * 64 + chunk * 16, p16);
+        tc::tmem_store_32x16(tmem_t1 + lane_base + half * 64 + chunk * 16, g16);
       }
       tc::tmem_store_wait();
       tc::tc_fence_before_sync();
@@ -291,14 +297,15 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
         T *out = which ? out1 : out0;
         const int64_t *stride = which ? shape.out1_stride : shape.out0_stride;
         const float factor = which ? 1.0f : shape.scale;
-        T *destination = out + batch * stride[0] + head * stride[1] + (int64_t)row * stride[2];
+        constexpr int kMine = kHeadDim / 2;                 // output columns per thread
+        T *destination = out + batch * stride[0] + head * stride[1] + (int64_t)row * stride[2] + half * kMine;
         const bool vector_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && stride[0] % 8 == 0 && stride[1] % 8 == 0 &&
                                stride[2] % 8 == 0;
 #pragma unroll 1
-        for (int chunk = 0; chunk < kHeadDim / 32; ++chunk) {
+        for (int chunk = 0; chunk < kMine / 32; ++chunk) {
           uint32_t raw[32];
           if (have) {
-            tc::tmem_load_32x32((which ? tmem_acc0 : tmem_acc1) + lane_base + chunk * 32, raw);
+            tc::tmem_load_32x32((which ? tmem_acc0 : tmem_acc1) + lane_base + half * kMine + chunk * 32, raw);
             tc::tmem_load_wait();
           } else {
 #pragma unroll
@@ -334,21 +341,39 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
   }
 }
 
-// delta[b, h, q] = sum_d f32(O) * f32(dO): one warp per row.
-template <typename T>
+// delta[b, h, q] = sum_d f32(O) * f32(dO).  LANES threads share a row, 8 elements (one 128-bit
+// access) per thread and pass; LANES = 1 is the scalar form for rows that are not 16-byte aligned.
+template <typename T, int LANES>
 __global__ void __launch_bounds__(256)
 attention_delta_kernel(const T *__restrict__ output, const T *__restrict__ grad_output, float *__restrict__ delta,
                        int64_t rows, int heads, int sequence, int head_dim, int64_t os0, int64_t os1, int64_t os2,
                        int64_t gs0, int64_t gs1, int64_t gs2, int64_t ds0, int64_t ds1, int64_t ds2) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
-    const int64_t b = row / ((int64_t)heads * sequence), h = (row / sequence) % heads, q = row % sequence;
-    const T *o = output + b * os0 + h * os1 + q * os2, *g = grad_output + b * gs0 + h * gs1 + q * gs2;
+  const int64_t thread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t threads = (int64_t)gridDim.x * blockDim.x;
+  const int lane = (int)(thread % LANES);
+  // the loop bound is the same for the 32 threads of a warp, so the shuffles below see whole warps
+  for (int64_t base = (thread - thread % 32) / LANES; base < rows; base += threads / LANES) {
+    const int64_t row = base + (thread % 32) / LANES;
     float sum = 0.0f;
-    for (int c = lane; c < head_dim; c += 32) sum += Element<T>::widen(o[c]) * Element<T>::widen(g[c]);
-    sum = warp_sum(sum);
-    if (lane == 0) delta[b * ds0 + h * ds1 + q * ds2] = sum;
+    int64_t b = 0, h = 0, q = 0;
+    if (row < rows) {
+      b = row / ((int64_t)heads * sequence); h = (row / sequence) % heads; q = row % sequence;
+      const T *o = output + b * os0 + h * os1 + q * os2, *g = grad_output + b * gs0 + h * gs1 + q * gs2;
+      if (LANES > 1) {
+        for (int c = lane * 8; c < head_dim; c += LANES * 8) {
+          float ov[8], gv[8];
+          load_vector<T>(o + c, ov);
+          load_vector<T>(g + c, gv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum += ov[i] * gv[i];
+        }
+      } else {
+        for (int c = 0; c < head_dim; ++c) sum += Element<T>::widen(o[c]) * Element<T>::widen(g[c]);
+      }
+    }
+#pragma unroll
+    for (int offset = LANES / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    if (lane == 0 && row < rows) delta[b * ds0 + h * ds1 + q * ds2] = sum;
   }
 }
 
@@ -523,19 +548,29 @@ extern "C" int b200_attention_backward_delta(B200_VIEW4(output), B200_VIEW4(grad
   if (!delta) return fail(B200_ERR_INVALID_ARGUMENT, "attention_backward_delta: null delta");
   if (o.extents[1] > INT32_MAX || o.extents[2] > INT32_MAX || o.extents[3] > INT32_MAX)
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "attention_backward_delta: extent too large");
-  const int64_t wanted = (rows + 7) / 8, limit = (int64_t)sm_count() * 8;
-  const unsigned grid = (unsigned)(wanted < limit ? wanted : limit);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_F16)
-    attention_delta_kernel<__half><<<grid, 256, 0, s>>>((const __half *)output, (const __half *)grad_output, (float *)delta, rows,
-                                                        (int)o.extents[1], (int)o.extents[2], (int)o.extents[3], output_s0,
-                                                        output_s1, output_s2, grad_output_s0, grad_output_s1, grad_output_s2,
-                                                        delta_s0, delta_s1, delta_s2);
-  else
-    attention_delta_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
-        (const __nv_bfloat16 *)output, (const __nv_bfloat16 *)grad_output, (float *)delta, rows, (int)o.extents[1],
-        (int)o.extents[2], (int)o.extents[3], output_s0, output_s1, output_s2, grad_output_s0, grad_output_s1,
-        grad_output_s2, delta_s0, delta_s1, delta_s2);
+  const int d = (int)o.extents[3];
+  const bool vectors = d % 8 == 0 && aligned16(output) && aligned16(grad_output) && output_s0 % 8 == 0 && output_s1 % 8 == 0 &&
+                       output_s2 % 8 == 0 && grad_output_s0 % 8 == 0 && grad_output_s1 % 8 == 0 && grad_output_s2 % 8 == 0;
+  const int lanes = !vectors ? 1 : d >= 128 ? 16 : d >= 64 ? 8 : d >= 32 ? 4 : d >= 16 ? 2 : 1;
+  const int64_t wanted = (rows * lanes + 255) / 256, limit = (int64_t)sm_count() * 8;
+  const unsigned grid = (unsigned)(wanted < limit ? wanted : limit);
+#define B200_DELTA(T, LANES)                                                                                         \
+  attention_delta_kernel<T, LANES><<<grid, 256, 0, s>>>((const T *)output, (const T *)grad_output, (float *)delta, rows, \
+                                                        (int)o.extents[1], (int)o.extents[2], d, output_s0, output_s1,   \
+                                                        output_s2, grad_output_s0, grad_output_s1, grad_output_s2,       \
+                                                        delta_s0, delta_s1, delta_s2)
+#define B200_DELTA_LANES(T)                              \
+  switch (lanes) {                                       \
+  case 16: B200_DELTA(T, 16); break;                     \
+  case 8: B200_DELTA(T, 8); break;                       \
+  case 4: B200_DELTA(T, 4); break;                       \
+  case 2: B200_DELTA(T, 2); break;                       \
+  default: B200_DELTA(T, 1); break;                      \
+  }
+  if (dtype == B200_F16) { B200_DELTA_LANES(__half) } else { B200_DELTA_LANES(__nv_bfloat16) }
+#undef B200_DELTA_LANES
+#undef B200_DELTA
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
