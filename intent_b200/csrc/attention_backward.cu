@@ -49,7 +49,7 @@ struct __align__(8) Barriers {
   uint64_t x_full, y_full[4], y_empty[4], t_full, g_ready, acc_full;
   uint32_t tmem_base;
   int abort_flag;
-  float columns[8][2][kTile / 2];   // MODE 0: [compute warp][lse*log2e | delta][its 64 query columns] of the current step
+  __align__(16) float columns[8][2][kTile / 2];   // MODE 0: [compute warp][lse*log2e | delta][its 64 query columns] of the current step
 };
 
 struct Shape {
@@ -264,20 +264,27 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
         tc::tmem_load_wait();
         uint32_t p16[16], g16[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p[2], g[2];
+        for (int quad = 0; quad < 8; ++quad) {   // four columns at a time: lse and delta come as 128-bit reads
+          float l[4] = {row_lse, row_lse, row_lse, row_lse}, d[4] = {row_delta, row_delta, row_delta, row_delta};
+          if (MODE == 0) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(&bars->columns[compute_warp][0][chunk * 32 + quad * 4]);
+            const float4 d4 = *reinterpret_cast<const float4 *>(&bars->columns[compute_warp][1][chunk * 32 + quad * 4]);
+            l[0] = l4.x; l[1] = l4.y; l[2] = l4.z; l[3] = l4.w;
+            d[0] = d4.x; d[1] = d4.y; d[2] = d4.z; d[3] = d4.w;
+          }
+          float p[4], g[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int mine = chunk * 32 + 2 * i + e, column = half * 64 + mine;
-            const float l = MODE == 0 ? bars->columns[compute_warp][0][mine] : row_lse;
-            const float d = MODE == 0 ? bars->columns[compute_warp][1][mine] : row_delta;
-            float probability = ex2_approx_ftz(fmaf(__uint_as_float(t0[2 * i + e]), shape.score_scale, -l));
+          for (int e = 0; e < 4; ++e) {
+            const int mine = chunk * 32 + quad * 4 + e, column = half * 64 + mine;
+            float probability = ex2_approx_ftz(fmaf(__uint_as_float(t0[quad * 4 + e]), shape.score_scale, -l[e]));
             if (masked && (MODE == 0 ? column < diagonal : column > diagonal)) probability = 0.0f;
             p[e] = probability;
-            g[e] = probability * (__uint_as_float(t1[2 * i + e]) - d);
+            g[e] = probability * (__uint_as_float(t1[quad * 4 + e]) - d[e]);
           }
-          p16[i] = pack_pair<T>(p[0], p[1]);
-          g16[i] = pack_pair<T>(g[0], g[1]);
+          p16[quad * 2] = pack_pair<T>(p[0], p[1]);
+          p16[quad * 2 + 1] = pack_pair<T>(p[2], p[3]);
+          g16[quad * 2] = pack_pair<T>(g[0], g[1]);
+          g16[quad * 2 + 1] = pack_pair<T>(g[2], g[3]);
         }
         // packed columns [64*half + 16*chunk, +16) lie over f32 columns this thread has already consumed
         if (MODE == 0) tc::tmem_store_32x16(tmem_t0 + lane_base + half * 64 + chunk * 16, p16);
