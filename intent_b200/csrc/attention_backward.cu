@@ -358,7 +358,9 @@ attention_delta_kernel(const T *__restrict__ output, const T *__restrict__ grad_
   const int64_t thread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t threads = (int64_t)gridDim.x * blockDim.x;
   const int lane = (int)(thread % LANES);
-  // the loop bound is the same for the 32 threads of a warp, so the shuffles below see whole warps
+  // the loop bound is the same for the 32 threads of a warp, so the shuffles below see whole warps;
+  // unrolled so that the loads of four rows are in flight together
+#pragma unroll 4
   for (int64_t base = (thread - thread % 32) / LANES; base < rows; base += threads / LANES) {
     const int64_t row = base + (thread % 32) / LANES;
     float sum = 0.0f;
