@@ -665,7 +665,7 @@ def run_reference(arguments, rank: int) -> None:
     milliseconds = (time.perf_counter() - begin) * 1e3 / arguments.steps
     value = case.workload.work / milliseconds / 1e6
     print(json.dumps({
-        "impl": "reference", "metric": "LayerNorm f16 forward throughput (algorithmic bytes / time)",
+        "impl": "reference", "metric": "layer_norm throughput (algorithmic bytes / time)",
         "value": value, "unit": "GB/s", "n_gpus": arguments.gpus, "steps": arguments.steps,
         "warmup": arguments.warmup, "ms_per_step": milliseconds, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
