@@ -386,6 +386,17 @@ attention_delta_kernel(const T *__restrict__ output, const T *__restrict__ grad_
   }
 }
 
+// With no query at all the key/value gradients are zero.
+template <typename T>
+__global__ void zero_view_kernel(T *out, int64_t total, int64_t heads, int64_t sequence, int64_t head_dim, int64_t s0,
+                                 int64_t s1, int64_t s2) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t d = i % head_dim, row = i / head_dim;
+    const int64_t b = row / (heads * sequence), h = (row / sequence) % heads, q = row % sequence;
+    out[b * s0 + h * s1 + q * s2 + d] = Element<T>::narrow(0.0f);
+  }
+}
+
 int tensor_map_4d(CUtensorMap *map, const void *base, const int64_t *extents, const int64_t *strides) {
   // innermost first: (D, S, H, B); a size-1 dimension may carry any stride, give TMA a legal one
   const uint64_t dims[4] = {(uint64_t)extents[3], (uint64_t)extents[2], (uint64_t)extents[1], (uint64_t)extents[0]};
@@ -413,6 +424,14 @@ int launch_backward(const View4 &q, const View4 &k, const View4 &v, const View4 
                     const View3 &delta, const View4 &out0, const View4 *out1, float scale, int head_group, int causal,
                     int *status, cudaStream_t stream) {
   using L = Layout<kHeadDim>;
+  if (MODE == 0 && q.extents[2] == 0) {
+    const int64_t total = k.extents[0] * k.extents[1] * k.extents[2] * kHeadDim;
+    for (const View4 *out : {&out0, out1})
+      zero_view_kernel<T><<<sm_count() * 4, 256, 0, stream>>>((T *)out->base, total, k.extents[1], k.extents[2], kHeadDim,
+                                                              out->strides[0], out->strides[1], out->strides[2]);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  }
   CUtensorMap map_q, map_k, map_v, map_g;
   int result = tensor_map_4d(&map_q, q.base, q.extents, q.strides);
   if (result == B200_OK) result = tensor_map_4d(&map_k, k.base, k.extents, k.strides);
@@ -455,7 +474,8 @@ int launch_backward(const View4 &q, const View4 &k, const View4 &v, const View4 
 int check_half_view(const char *entry, const char *name, const View4 &view, bool tma) {
   for (int i = 0; i < 4; ++i)
     if (view.extents[i] < 0) return fail(B200_ERR_INVALID_ARGUMENT, "%s: %s has a negative extent", entry, name);
-  if (!view.base) return fail(B200_ERR_INVALID_ARGUMENT, "%s: %s is null", entry, name);
+  const bool empty = view.extents[0] == 0 || view.extents[1] == 0 || view.extents[2] == 0 || view.extents[3] == 0;
+  if (!view.base && !empty) return fail(B200_ERR_INVALID_ARGUMENT, "%s: %s is null", entry, name);
   if (view.extents[3] > 1 && view.strides[3] != 1)
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "%s: %s must have unit innermost stride", entry, name);
   if (tma) {
@@ -498,7 +518,8 @@ int backward_entry(const char *entry, int mode, const View4 &q, const View4 &k, 
     return fail(B200_ERR_INVALID_ARGUMENT, "%s: q, grad_output (B,HQ,Q,D), k, v (B,HK,K,D), lse, delta (B,HQ,Q), HQ = HK * head_group", entry);
   if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_INVALID_ARGUMENT, "%s: element type %d is not f16/bf16", entry, dtype);
   if (d != 64 && d != 128) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "%s: head dimension must be 64 or 128 (got %lld)", entry, (long long)d);
-  if (!lse.base || !delta.base) return fail(B200_ERR_INVALID_ARGUMENT, "%s: null lse or delta", entry);
+  if (b * hq * sq == 0 && (mode == 1 || b * hk * sk == 0)) return B200_OK;      // nothing to write
+  if (b * hq * sq != 0 && (!lse.base || !delta.base)) return fail(B200_ERR_INVALID_ARGUMENT, "%s: null lse or delta", entry);
   if (!workspace || ws_d0 < B200_WORKSPACE_WORDS || (ws_d0 > 1 && ws_s0 != 1))
     return fail(B200_ERR_INVALID_ARGUMENT, "%s: workspace must hold %d contiguous int32 words", entry, B200_WORKSPACE_WORDS);
   if (sq > INT32_MAX - 256 || sk > INT32_MAX - 256 || hq > 65535 || b > 65535)

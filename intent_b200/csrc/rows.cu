@@ -359,17 +359,28 @@ template <typename T> bool plan_row(int64_t columns, RowPlan *plan) {
 }
 
 // CTAs of `kernel` that are resident per SM (register, thread and shared-memory limits),
-// so the persistent grid is exactly one wave.  Cached per kernel and shared-memory size.
+// so the persistent grid is exactly one wave.  The last answer is cached per thread, keyed by the
+// kernel's address (instantiations that differ only in integer parameters share one function
+// type, so a cache per template instance of this helper would mix them up), the CTA size, the
+// shared-memory size and the device.
 template <typename Kernel>
 int resident_ctas(Kernel kernel, int threads, size_t smem) {
-  static thread_local size_t cached_smem = ~size_t(0);
+  struct Key {
+    const void *kernel;
+    int threads, device;
+    size_t smem;
+  };
+  static thread_local Key cached_key = {nullptr, 0, -1, 0};
   static thread_local int cached = 0;
-  if (cached_smem != smem) {
+  int device = 0;
+  cudaGetDevice(&device);
+  const void *address = reinterpret_cast<const void *>(kernel);
+  if (cached_key.kernel != address || cached_key.threads != threads || cached_key.smem != smem || cached_key.device != device) {
     int blocks = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, smem) != cudaSuccess || blocks < 1)
       blocks = 1;
     cached = blocks;
-    cached_smem = smem;
+    cached_key = {address, threads, device, smem};
   }
   return cached;
 }
@@ -562,9 +573,7 @@ extern "C" int b200_softmax_backward(const void *p, int64_t p_d0, int64_t p_d1, 
   if (same_alignment && p_d1 <= 8 * 1024) {
     const int per_thread = (int)((p_d1 / 4 + 255) / 256);
     auto launch = [&](auto kernel) {
-      int resident = 0;   // not resident_ctas(): the four instantiations share one function type, hence one cache
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, 0) != cudaSuccess || resident < 1) resident = 1;
-      const int64_t limit = (int64_t)sm_count() * resident;
+      const int64_t limit = (int64_t)sm_count() * resident_ctas(kernel, 256, 0);
       kernel<<<(unsigned)(p_d0 < limit ? p_d0 : limit), 256, 0, queue>>>((const float *)p, (const float *)dy, (float *)dx,
                                                                         p_d0, (int)p_d1, p_s0, u_s0, g_s0);
     };

@@ -314,6 +314,48 @@ def test_attention_backward_argument_errors():
         ops.attention_backward_dkdv(*cuda(q, k, v, grad_output, lse), delta, scale, head_group=1)
 
 
+def test_backward_kernels_accept_empty_operands():
+    """Zero-sized operands are not errors anywhere in the reference's binders; nothing is launched."""
+    empty = torch.empty((0, 64), dtype=torch.bfloat16, device=DEV)
+    partial = torch.ones((4, 64), dtype=torch.bfloat16, device=DEV)
+    stats = torch.empty((0,), device=DEV)
+    dx = ops.layer_norm_backward_rows(empty, empty, torch.ones(64, dtype=torch.bfloat16, device=DEV), stats, stats,
+                                      partial, partial.clone(), 1.0 / 64)
+    assert dx.shape == (0, 64) and torch.equal(partial, torch.ones_like(partial))
+    none = torch.empty((0, 8), dtype=torch.bfloat16, device=DEV)
+    dw, db = ops.layer_norm_backward_reduce(none, none)
+    assert torch.equal(dw, torch.zeros(8, device=DEV)) and torch.equal(db, torch.zeros(8, device=DEV))
+    q = torch.empty((0, 2, 16, 64), dtype=torch.float16, device=DEV)
+    k = torch.empty((0, 1, 16, 64), dtype=torch.float16, device=DEV)
+    rows = torch.empty((0, 2, 16), device=DEV)
+    assert ops.attention_backward_delta(q, q).shape == (0, 2, 16)
+    assert ops.attention_backward_dq(q, k, k, q, rows, rows, 0.125, head_group=2).shape == q.shape
+    grad_k, grad_v = ops.attention_backward_dkdv(q, k, k, q, rows, rows, 0.125, head_group=2)
+    assert grad_k.shape == k.shape and grad_v.shape == k.shape
+    assert ops.softmax_backward(torch.empty((0, 5), device=DEV), torch.empty((0, 5), device=DEV)).shape == (0, 5)
+    # keys but no query: the key/value gradients are zero
+    q = torch.empty((1, 2, 0, 64), dtype=torch.float16, device=DEV)
+    k = torch.randn((1, 1, 40, 64), device=DEV).half()
+    rows = torch.empty((1, 2, 0), device=DEV)
+    grad_k, grad_v = ops.attention_backward_dkdv(q, k, k, q, rows, rows, 0.125, head_group=2)
+    assert not grad_k.any() and not grad_v.any()
+
+
+def test_attention_backward_keys_shorter_than_queries():
+    """Causal tiles past the last key are skipped; query tiles past the last query write zeros."""
+    q, k, v, output, grad_output, lse, scale = workloads.attention_backward_inputs(1, 2, 1, 300, 64, seed=9, keys=140)
+    delta = ops.attention_backward_delta(*cuda(output, grad_output))
+    device = cuda(q, k, v, grad_output, lse)
+    grad_k, grad_v = ops.attention_backward_dkdv(*device, delta, scale, head_group=2)
+    grad_q = ops.attention_backward_dq(*device, delta, scale, head_group=2)
+    expected_delta = oracle.attention_backward_delta(output, grad_output)
+    expected_k, expected_v = oracle.attention_backward_dkdv(q, k, v, grad_output, lse, expected_delta, scale, head_group=2)
+    expected_q = oracle.attention_backward_dq(q, k, v, grad_output, lse, expected_delta, scale, head_group=2)
+    assert relative_error(grad_q, expected_q) <= 1e-2
+    assert relative_error(grad_k, expected_k) <= 1e-2
+    assert relative_error(grad_v, expected_v) <= 1e-2
+
+
 COLUMN_BLOCK_SCRIPT = """
 import sys, torch
 sys.path.insert(0, %r)
