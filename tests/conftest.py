@@ -9,7 +9,8 @@ ROOT = Path(__file__).resolve().parents[1]
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-REFERENCE_PYTHON = Path(os.environ.get("INTENT_REFERENCE", "/root/reference")) / "python"
+# the reference checkout: named by INTENT_REFERENCE, else looked for beside this repository
+REFERENCE_PYTHON = Path(os.environ.get("INTENT_REFERENCE", ROOT.parent / "reference")) / "python"
 
 
 def pytest_configure(config):
