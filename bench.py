@@ -6,16 +6,19 @@
 One JSON line on stdout.  A "step" is one launch of the operator over one
 batch of seeded synthetic input (``intent_b200.workloads``).  The headline
 workload is the LayerNorm configuration (f16 16384 x 4096, 268 MB per step, larger
-than L2); ``--op all`` (the default) also measures softmax, GEMM, attention and
-CSR SpMM and reports them under ``"ops"``.
+than L2); ``--op all`` (the default) also measures softmax, GEMM, attention, CSR SpMM
+and the widened kernels (SpMV, softmax / LayerNorm / attention backward) and reports
+them under ``"ops"``.
 
   value     device-resident throughput: inputs already in HBM, K launches timed with
             CUDA events on the launching stream between two barriers + syncs,
             max over ranks, whole-job aggregate (weak scaling: each rank runs the
             full per-GPU workload, no data-path collective).
-  e2e       the same metric through the public API (jit(...).prepare(...).launch())
-            with HOST buffers: pinned host -> device copy of the step's inputs and a
-            device -> host read of its output inside the timed region.
+  e2e       the same metric through the public API (jit(...).prepare(...), then
+            call.enqueue(stream)) with HOST buffers: every step copies its inputs from
+            pinned host memory and its result back inside the timed region; the copies
+            of neighbouring steps overlap on three streams over two sets of device
+            buffers, and the region ends when the last result is in host memory.
   roofline  achieved = algorithmic bytes (or flops) per launch / average launch time,
             against the pod-measured peak in MEASURED_PEAKS.json.
   cpu_baseline  the CPU oracle (a port of the reference's kernel definitions; the
@@ -155,6 +158,69 @@ def pinned(tensor: torch.Tensor) -> torch.Tensor:
     return tensor.contiguous().pin_memory()
 
 
+class PipelinedEndToEnd:
+    """End-to-end steps through the artifact API with the copies of neighbouring steps overlapped, the
+    way a throughput caller uses `B200Call.enqueue(stream)`: step i's host-to-device copy, its launch
+    and its device-to-host copy run on three streams, over two sets of device buffers, so the PCIe
+    link carries both directions at once.  Every step still copies its own inputs in and its own
+    result out; the timed region ends when the last result has landed in pinned host memory."""
+
+    def __init__(self, kernel, host_inputs, scalars, device, adapt=None, build=None):
+        """One kernel: `kernel.prepare(*device buffers, *scalars)`, its result travels back.  Several:
+        `build(device buffers)` returns the prepared calls in launch order and the tensors that travel back."""
+        self.host_in = [pinned(t) for t in host_inputs]
+        self.slots = []
+        for _ in range(2):
+            device_in = [torch.empty_like(t, device=device) for t in host_inputs]
+            if build is not None:
+                calls, results = build(device_in)
+            else:
+                call = kernel.prepare(*(adapt(device_in) if adapt else device_in), *scalars)
+                calls, results = [call], [call.result()]
+            self.slots.append((device_in, calls, results))
+        self.host_out = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in self.slots[0][2]]
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(3)]   # in, launch, out
+        self.copied_in = [torch.cuda.Event() for _ in range(2)]
+        self.launched = [torch.cuda.Event() for _ in range(2)]
+        self.copied_out = [torch.cuda.Event() for _ in range(2)]
+        self.h2d = sum(t.numel() * t.element_size() for t in host_inputs)
+        self.d2h = sum(r.numel() * r.element_size() for r in self.slots[0][2])
+        self.used = [False, False]
+
+    def step(self, index: int) -> None:
+        slot = index % 2
+        device_in, calls, results = self.slots[slot]
+        copy_in, launch, copy_out = self.streams
+        with torch.cuda.stream(copy_in):
+            if self.used[slot]:
+                copy_in.wait_event(self.launched[slot])      # the launch two steps ago has read these buffers
+            for target, source in zip(device_in, self.host_in):
+                target.copy_(source, non_blocking=True)
+            self.copied_in[slot].record(copy_in)
+        launch.wait_event(self.copied_in[slot])
+        if self.used[slot]:
+            launch.wait_event(self.copied_out[slot])         # its result has left the output buffer
+        for call in calls:
+            call.enqueue(launch)
+        self.launched[slot].record(launch)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(self.launched[slot])
+            for target, source in zip(self.host_out, results):
+                target.copy_(source, non_blocking=True)
+            self.copied_out[slot].record(copy_out)
+        self.used[slot] = True
+
+    def begin(self) -> None:
+        """After the start event: the three streams start behind the current stream."""
+        for stream in self.streams:
+            stream.wait_stream(torch.cuda.current_stream())
+
+    def finish(self) -> None:
+        """Before the stop event: the current stream waits until the last result is in host memory."""
+        for stream in self.streams:
+            torch.cuda.current_stream().wait_stream(stream)
+
+
 class SoftmaxCase(Case):
     name = "softmax"
 
@@ -168,19 +234,15 @@ class SoftmaxCase(Case):
         self.sets = [(self.host_x.to(device) + 0, torch.empty(4096, 1024, device=device)) for _ in range(12)]
         self.flush = "rotating 12 buffer pairs (384 MB > L2)"
         self.kernel = b200.jit(b200.kernels.stable_softmax)
-        self.host_in, self.host_out = pinned(self.host_x), torch.empty(4096, 1024).pin_memory()
-        self.dev_in = torch.empty(4096, 1024, device=device)
-        self.call = self.kernel.prepare(self.dev_in)
-        self.h2d, self.d2h = self.host_in.numel() * 4, self.host_out.numel() * 4
+        self.pipeline = PipelinedEndToEnd(self.kernel, [self.host_x], (), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         x, y = self.sets[step % len(self.sets)]
         self.ops.softmax(x, out=y)
 
     def e2e(self, step):
-        self.dev_in.copy_(self.host_in, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         return lambda: oracle.softmax(self.host_x, workers=workers), 1.0, "full workload (4096 rows)"
@@ -200,18 +262,15 @@ class LayerNormCase(Case):
         self.y = torch.empty_like(self.x)
         self.flush = "inputs larger than L2 (268 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.layer_norm_f16)
-        self.host_in, self.host_out = pinned(x), torch.empty_like(x).pin_memory()
-        self.dev_in = torch.empty_like(self.x)
-        self.call = self.kernel.prepare(self.dev_in, self.w, self.b, self.inv, self.eps)
-        self.h2d, self.d2h = x.numel() * 2, x.numel() * 2
+        # x travels every step; gamma and beta are parameters that stay on the device
+        self.pipeline = PipelinedEndToEnd(self.kernel, [x], (self.w, self.b, self.inv, self.eps), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.layer_norm(self.x, self.w, self.b, self.inv, self.eps, out=self.y)
 
     def e2e(self, step):
-        self.dev_in.copy_(self.host_in, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         x, w, b, inv, eps = self.host
@@ -232,21 +291,16 @@ class GemmCase(Case):
         self.c = torch.empty(8192, 8192, dtype=torch.float16, device=device)
         self.flush = "inputs larger than L2 (403 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.gemm, constexprs={"ACTIVATION": "NONE"})
-        self.host_in_a, self.host_in_b = pinned(a), pinned(b.t())
-        self.dev_a = torch.empty_like(self.a)
-        self.dev_bt = torch.empty(8192, 8192, dtype=torch.float16, device=device)
-        self.host_out = torch.empty(8192, 8192, dtype=torch.float16).pin_memory()
-        self.call = self.kernel.prepare(self.dev_a, self.dev_bt.t())
-        self.h2d, self.d2h = 2 * 8192 * 8192 * 2, 8192 * 8192 * 2
+        # B travels in its column-major storage (the transposed matrix is the contiguous one)
+        self.pipeline = PipelinedEndToEnd(self.kernel, [a, b.t().contiguous()], (), device,
+                                          adapt=lambda buffers: (buffers[0], buffers[1].t()))
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.gemm(self.a, self.b, out=self.c)
 
     def e2e(self, step):
-        self.dev_a.copy_(self.host_in_a, non_blocking=True)
-        self.dev_bt.copy_(self.host_in_b, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         rows = 64
@@ -269,20 +323,14 @@ class AttentionCase(Case):
         self.o = torch.empty_like(self.q)
         self.flush = "inputs larger than L2 (1074 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.flash_attention_bf16_fwd, constexprs={"HEAD_GROUP": 1, "CAUSAL": True})
-        self.host_in = [pinned(t) for t in (q, k, v)]
-        self.dev_in = [torch.empty_like(self.q) for _ in range(3)]
-        self.host_out = torch.empty_like(q).pin_memory()
-        self.call = self.kernel.prepare(*self.dev_in, self.scale)
-        self.h2d, self.d2h = 3 * q.numel() * 2, q.numel() * 2
+        self.pipeline = PipelinedEndToEnd(self.kernel, [q, k, v], (self.scale,), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.flash_attention(self.q, self.k, self.v, self.scale, out=self.o)
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         q, k, v = self.host
@@ -306,21 +354,14 @@ class SpmmCase(Case):
         self.y = torch.empty(262144, 128, device=device)
         self.flush = "inputs larger than L2 (337 MB compulsory per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.csr_spmm_262144)
-        self.host_in = [pinned(t) for t in self.host]
-        self.dev_in = [torch.empty_like(t) for t in self.dev]
-        self.host_out = torch.empty(262144, 128).pin_memory()
-        self.call = self.kernel.prepare(*self.dev_in)
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
-        self.d2h = self.host_out.numel() * 4
+        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.csr_spmm(*self.dev, out=self.y)
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         return lambda: oracle.csr_spmm(*self.host, workers=workers), 1.0, "full workload (262144 rows)"
@@ -339,20 +380,14 @@ class SoftmaxBackwardCase(Case):
         self.g = torch.empty_like(self.p)
         self.flush = "inputs larger than L2 (201 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.softmax_backward)
-        self.host_in = [pinned(t) for t in self.host]
-        self.dev_in = [torch.empty_like(self.p) for _ in range(2)]
-        self.host_out = torch.empty_like(self.host[0]).pin_memory()
-        self.call = self.kernel.prepare(*self.dev_in)
-        self.h2d, self.d2h = 2 * self.p.numel() * 4, self.p.numel() * 4
+        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.softmax_backward(self.p, self.u, out=self.g)
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         return lambda: oracle.softmax_backward(*self.host, workers=workers), 1.0, "full workload (4096 rows)"
@@ -372,22 +407,15 @@ class SpmvCase(Case):
         self.sets = [[t.to(device) + 0 for t in self.host] + [torch.empty(32768, device=device)] for _ in range(20)]
         self.flush = "rotating 20 copies of the operands (172 MB > L2)"
         self.kernel = b200.jit(b200.kernels.csr_spmv)
-        self.host_in = [pinned(t) for t in self.host]
-        self.dev_in = [torch.empty_like(t) for t in self.sets[0][:4]]
-        self.host_out = torch.empty(32768).pin_memory()
-        self.call = self.kernel.prepare(*self.dev_in)
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
-        self.d2h = 32768 * 4
+        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         ro, ci, va, x, y = self.sets[step % len(self.sets)]
         self.ops.csr_spmv(ro, ci, va, x, out=y)
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.call.launch()
-        self.host_out.copy_(self.call.result(), non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         return lambda: oracle.csr_spmv(*self.host, workers=workers), 1.0, "full workload (32768 rows)"
@@ -414,14 +442,13 @@ class LayerNormBackwardCase(Case):
         self.flush = "rotating three copies of the operands (302 MB > L2)"
         self.rows = b200.jit(b200.kernels.layer_norm_backward_rows)
         self.reduce = b200.jit(b200.kernels.layer_norm_backward_reduce)
-        self.host_in = [pinned(t) for t in self.host]
-        self.dev_in = [torch.empty_like(t) for t in self.dev]
-        self.rows_call = self.rows.prepare(*self.dev_in, self.inverse)
-        self.reduce_call = self.reduce.prepare(self.dev_in[5], self.dev_in[6])
-        self.host_out = [torch.empty_like(self.host[0]).pin_memory(), torch.empty(4096).pin_memory(),
-                         torch.empty(4096).pin_memory()]
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
-        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+
+        def build(buffers):
+            rows_call = self.rows.prepare(*buffers, self.inverse)
+            reduce_call = self.reduce.prepare(buffers[5], buffers[6])
+            return [rows_call, reduce_call], [rows_call.result(), *reduce_call.result()]
+        self.pipeline = PipelinedEndToEnd(None, list(self.host), (), device, build=build)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         *operands, dx = self.sets[step % len(self.sets)]
@@ -429,13 +456,7 @@ class LayerNormBackwardCase(Case):
         self.ops.layer_norm_backward_reduce(operands[5], operands[6], dw=self.dw, db=self.db)
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.rows_call.launch()
-        self.reduce_call.launch()
-        dw, db = self.reduce_call.result()
-        for host, dev in zip(self.host_out, (self.rows_call.result(), dw, db)):
-            host.copy_(dev, non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         x, dy, w, mean, rstd, dw_partial, db_partial = self.host
@@ -464,16 +485,18 @@ class AttentionBackwardCase(Case):
         self.grads = [torch.empty_like(self.dev[0]), torch.empty_like(self.dev[1]), torch.empty_like(self.dev[2])]
         self.flush = "inputs larger than L2 (503 MB of operands and gradients per step vs 126 MB)"
         options = {"HEAD_GROUP": 4, "CAUSAL": True}
-        self.host_in = [pinned(t) for t in self.host]
-        self.dev_in = [torch.empty_like(t) for t in self.dev]
-        qd, kd, vd, od, gd, ld = self.dev_in
-        self.delta_call = b200.jit(b200.kernels.attention_backward_delta).prepare(od, gd)
-        common = (qd, kd, vd, gd, ld, self.delta_call.result(), self.scale)
-        self.dkdv_call = b200.jit(b200.kernels.attention_backward_dkdv, constexprs=options).prepare(*common)
-        self.dq_call = b200.jit(b200.kernels.attention_backward_dq, constexprs=options).prepare(*common)
-        self.host_out = [torch.empty_like(t).pin_memory() for t in (q, k, v)]
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host)
-        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+        kernels = (b200.jit(b200.kernels.attention_backward_delta),
+                   b200.jit(b200.kernels.attention_backward_dkdv, constexprs=options),
+                   b200.jit(b200.kernels.attention_backward_dq, constexprs=options))
+
+        def build(buffers):
+            qd, kd, vd, od, gd, ld = buffers
+            delta_call = kernels[0].prepare(od, gd)
+            common = (qd, kd, vd, gd, ld, delta_call.result(), self.scale)
+            dkdv_call, dq_call = kernels[1].prepare(*common), kernels[2].prepare(*common)
+            return [delta_call, dkdv_call, dq_call], [dq_call.result(), *dkdv_call.result()]
+        self.pipeline = PipelinedEndToEnd(None, list(self.host), (), device, build=build)
+        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         q, k, v, output, grad_output, lse = self.dev
@@ -484,14 +507,7 @@ class AttentionBackwardCase(Case):
                                        grad_q=self.grads[0])
 
     def e2e(self, step):
-        for dev, host in zip(self.dev_in, self.host_in):
-            dev.copy_(host, non_blocking=True)
-        self.delta_call.launch()
-        self.dkdv_call.launch()
-        self.dq_call.launch()
-        grad_k, grad_v = self.dkdv_call.result()
-        for host, dev in zip(self.host_out, (self.dq_call.result(), grad_k, grad_v)):
-            host.copy_(dev, non_blocking=True)
+        self.pipeline.step(step)
 
     def cpu(self, oracle, workers):
         # batch 0, key head 0 with its four query heads: 1 of the 64 (batch, key head) groups
@@ -524,15 +540,24 @@ def max_over_ranks(value: float, distributed: bool, device) -> float:
     return float(tensor.item())
 
 
-def timed(function, steps: int, warmup: int, distributed: bool, device) -> float:
-    """Milliseconds per step: CUDA events on the current (launching) stream, max over ranks."""
+def timed(function, steps: int, warmup: int, distributed: bool, device, begin=None, finish=None) -> float:
+    """Milliseconds per step: CUDA events on the current (launching) stream, max over ranks.  A
+    function that spreads its work over other streams gives `begin` (run after the start event: its
+    streams wait for the current one) and `finish` (run before the stop event: the current stream
+    waits for them), so the two events bracket all of it."""
     for step in range(warmup):
         function(step)
+    if finish:
+        finish()
     barrier(distributed)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
+    if begin:
+        begin()
     for step in range(steps):
         function(warmup + step)
+    if finish:
+        finish()
     stop.record()
     barrier(distributed)
     return max_over_ranks(start.elapsed_time(stop), distributed, device) / steps
@@ -611,7 +636,10 @@ def measure(case, steps: int, warmup: int, distributed: bool, world: int, peak_t
     resident_ms = timed_graph(case.launch, steps, warmup, distributed, case.device)
     time.sleep(0.06)  # let the sampler deliver the sample that covers the end of the window
     own_clocks = CLOCKS.summary(CLOCKS.windows[first_window:]) if CLOCKS is not None else None
-    e2e_ms = timed(case.e2e, max(2, steps // 4), 1, distributed, case.device)
+    pipeline = getattr(case, "pipeline", None)
+    # a two-deep pipeline needs enough steps for its fill and drain not to dominate
+    e2e_ms = timed(case.e2e, steps if pipeline else max(2, steps // 4), 2 if pipeline else 1, distributed, case.device,
+                   begin=pipeline.begin if pipeline else None, finish=pipeline.finish if pipeline else None)
     per_gpu = workload.work / resident_ms / scale
     if workload.bound == "hbm":
         peak, peak_name = peak_table["hbm_gbs"], f"{peak_kind} STREAM-style copy"
@@ -730,7 +758,8 @@ def main() -> None:
                                         with_cpu=(rank == 0 and world == 1))
                 # warm-up, the captured pass, the timed replay (the 0.25 s of load replays before it
                 # are not counted), then the end-to-end warm-up and steps
-                launches += case.launches_per_step * (arguments.warmup + 3 * steps + 1 + max(2, steps // 4))
+                end_to_end = (steps + 2) if hasattr(case, "pipeline") else (1 + max(2, steps // 4))
+                launches += case.launches_per_step * (arguments.warmup + 3 * steps + end_to_end)
                 del case
             except Exception as error:  # one failing operator must not hide the others
                 if name == primary:
