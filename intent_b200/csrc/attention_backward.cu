@@ -45,8 +45,8 @@ template <int kHeadDim> struct Layout {
   static constexpr int kStages = kHeadDim == 64 ? 4 : 2;
 };
 
-struct __align__(8) Barriers {
-  uint64_t x_full, y_full[4], y_empty[4], t_full, g_ready, acc_full;
+struct __align__(16) Barriers {
+  uint64_t x_full, y_full[4], y_empty[4], t0_full, t1_full, p_ready, g_ready, acc_full;
   uint32_t tmem_base;
   int abort_flag;
   __align__(16) float columns[8][2][kTile / 2];   // MODE 0: [compute warp][lse*log2e | delta][its 64 query columns] of the current step
@@ -114,7 +114,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
       tc::mbar_init(&bars->y_full[s], 1);
       tc::mbar_init(&bars->y_empty[s], 1);
     }
-    tc::mbar_init(&bars->t_full, 1);
+    tc::mbar_init(&bars->t0_full, 1);
+    tc::mbar_init(&bars->t1_full, 1);
+    tc::mbar_init(&bars->p_ready, 8);
     tc::mbar_init(&bars->g_ready, 8);
     tc::mbar_init(&bars->acc_full, 1);
     bars->abort_flag = 0;
@@ -180,36 +182,56 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
       const uint32_t x_address = tc::smem_u32(x_tiles), ring_address = tc::smem_u32(ring);
       bool alive = tc::mbar_wait(&bars->x_full, 0, abort_flag, status, tc::kSiteMmaFull);
       tc::tc_fence_after_sync();
-      for (int step = 0; alive && step < steps; ++step) {
-        const int stage = step % kStages;
-        if (!tc::mbar_wait(&bars->y_full[stage], (step / kStages) & 1, abort_flag, status, tc::kSiteMmaFull)) break;
-        tc::tc_fence_after_sync();
-        const uint32_t y_address = ring_address + stage * 2 * L::kTileBytes;
+      // T0 = X0 . Y0^T or T1 = X1 . Y1^T of one step
+      auto issue_scores = [&](int which, int step) {
+        const uint32_t y_address = ring_address + (step % kStages) * 2 * L::kTileBytes;
 #pragma unroll
-        for (int which = 0; which < 2; ++which) {               // T0 = X0 . Y0^T, T1 = X1 . Y1^T
-#pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-            const uint32_t offset = which * L::kTileBytes + (kk / 4) * L::kHalfBytes + (kk % 4) * 32;
-            tc::mma_f16_ss(which ? tmem_t1 : tmem_t0, tc::smem_desc_k_major_sw128(x_address + offset),
-                           tc::smem_desc_k_major_sw128(y_address + offset), idesc_t, kk != 0);
-          }
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+          const uint32_t offset = which * L::kTileBytes + (kk / 4) * L::kHalfBytes + (kk % 4) * 32;
+          tc::mma_f16_ss(which ? tmem_t1 : tmem_t0, tc::smem_desc_k_major_sw128(x_address + offset),
+                         tc::smem_desc_k_major_sw128(y_address + offset), idesc_t, kk != 0);
         }
-        tc::mma_commit(&bars->t_full);
-        if (!tc::mbar_wait(&bars->g_ready, step & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
-        tc::tc_fence_after_sync();
+        tc::mma_commit(which ? &bars->t1_full : &bars->t0_full);
+      };
+      // acc += (P or G, 16 bits, in TMEM) . (Y1 or Y0 of the step, as an MN-major B operand)
+      auto issue_gradient = [&](uint32_t accumulator, uint32_t operand, int which_y, int step) {
+        const uint32_t y_address = ring_address + (step % kStages) * 2 * L::kTileBytes + which_y * L::kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          // B: the same 16 rows of Y, 2048 bytes apart
-          // key block kk (16 streamed rows, 8 packed columns) was written by column half kk/4 into its own columns
-          tc::mma_f16_ts(tmem_acc1, tmem_t1 + (kk / 4) * 64 + (kk % 4) * 8,
+          // key block kk (16 streamed rows, 8 packed columns) was written by column half kk/4 into its own
+          // columns; B: the same 16 rows of Y, 2048 bytes apart
+          tc::mma_f16_ts(accumulator, operand + (kk / 4) * 64 + (kk % 4) * 8,
                          tc::smem_desc_mn_major_sw128(y_address + kk * 2048, L::kHalfBytes), idesc_acc, (step | kk) != 0);
-          if (MODE == 0)
-            tc::mma_f16_ts(tmem_acc0, tmem_t0 + (kk / 4) * 64 + (kk % 4) * 8,
-                           tc::smem_desc_mn_major_sw128(y_address + L::kTileBytes + kk * 2048, L::kHalfBytes), idesc_acc,
-                           (step | kk) != 0);
         }
-        tc::mma_commit(&bars->y_empty[stage]);
-        if (step == steps - 1) tc::mma_commit(&bars->acc_full);
+      };
+      auto wait_stage = [&](int step) {
+        const bool ok = tc::mbar_wait(&bars->y_full[step % kStages], (step / kStages) & 1, abort_flag, status, tc::kSiteMmaFull);
+        tc::tc_fence_after_sync();
+        return ok;
+      };
+      // The score products of step i+1 are issued as soon as their TMEM tile is free again, so they
+      // (and the gradient products of step i) run while the compute warps are busy:
+      //   P(i) ready -> dV += P.dO (MODE 0) -> T0 is free: S(i+1)
+      //   G(i) ready -> acc1 += G.Y0        -> T1 is free: dP(i+1)
+      if (alive && wait_stage(0)) {
+        issue_scores(0, 0);
+        issue_scores(1, 0);
+        for (int step = 0; step < steps; ++step) {
+          const bool more = step + 1 < steps;
+          if (!tc::mbar_wait(&bars->p_ready, step & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
+          tc::tc_fence_after_sync();
+          if (MODE == 0) issue_gradient(tmem_acc0, tmem_t0, 1, step);
+          if (more) {
+            if (!wait_stage(step + 1)) break;
+            issue_scores(0, step + 1);
+          }
+          if (!tc::mbar_wait(&bars->g_ready, step & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
+          tc::tc_fence_after_sync();
+          issue_gradient(tmem_acc1, tmem_t1, 0, step);
+          tc::mma_commit(&bars->y_empty[step % kStages]);      // both gradient products of the step have read its tiles
+          if (more) issue_scores(1, step + 1);
+          else tc::mma_commit(&bars->acc_full);
+        }
       }
     }
   } else {
@@ -249,45 +271,68 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
         }
         __syncwarp();
       }
-      if (!tc::mbar_wait(&bars->t_full, parity, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
-      tc::tc_fence_after_sync();
       // column c of the tile is excluded when its key lies after its query
       //   MODE 0: key = row, query = streamed0 + c  -> excluded when c < row - streamed0
       //   MODE 1: key = streamed0 + c, query = row  -> excluded when c > row - streamed0
       const int diagonal = row - streamed0;
       const bool masked = shape.causal && (MODE == 0 ? streamed0 < row0 + kTile - 1 : streamed0 + kTile - 1 > row0);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kTile / 64; ++chunk) {
-        uint32_t t0[32], t1[32];
-        tc::tmem_load_32x32(tmem_t0 + lane_base + half * 64 + chunk * 32, t0);
-        tc::tmem_load_32x32(tmem_t1 + lane_base + half * 64 + chunk * 32, t1);
-        tc::tmem_load_wait();
-        uint32_t p16[16], g16[16];
+      // phase A: P from T0, kept in registers for phase B; its 16-bit copy goes back over T0 (MODE 0)
+      float probability[kTile / 2];
+      if (!tc::mbar_wait(&bars->t0_full, parity, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
+      tc::tc_fence_after_sync();
 #pragma unroll
-        for (int quad = 0; quad < 8; ++quad) {   // four columns at a time: lse and delta come as 128-bit reads
-          float l[4] = {row_lse, row_lse, row_lse, row_lse}, d[4] = {row_delta, row_delta, row_delta, row_delta};
+      for (int chunk = 0; chunk < kTile / 64; ++chunk) {
+        uint32_t t0[32];
+        tc::tmem_load_32x32(tmem_t0 + lane_base + half * 64 + chunk * 32, t0);
+        tc::tmem_load_wait();
+        uint32_t p16[16];
+#pragma unroll
+        for (int quad = 0; quad < 8; ++quad) {   // four columns at a time: lse comes as one 128-bit read
+          float l[4] = {row_lse, row_lse, row_lse, row_lse};
           if (MODE == 0) {
             const float4 l4 = *reinterpret_cast<const float4 *>(&bars->columns[compute_warp][0][chunk * 32 + quad * 4]);
-            const float4 d4 = *reinterpret_cast<const float4 *>(&bars->columns[compute_warp][1][chunk * 32 + quad * 4]);
             l[0] = l4.x; l[1] = l4.y; l[2] = l4.z; l[3] = l4.w;
-            d[0] = d4.x; d[1] = d4.y; d[2] = d4.z; d[3] = d4.w;
           }
-          float p[4], g[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int mine = chunk * 32 + quad * 4 + e, column = half * 64 + mine;
-            float probability = ex2_approx_ftz(fmaf(__uint_as_float(t0[quad * 4 + e]), shape.score_scale, -l[e]));
-            if (masked && (MODE == 0 ? column < diagonal : column > diagonal)) probability = 0.0f;
-            p[e] = probability;
-            g[e] = probability * (__uint_as_float(t1[quad * 4 + e]) - d[e]);
+            float p = ex2_approx_ftz(fmaf(__uint_as_float(t0[quad * 4 + e]), shape.score_scale, -l[e]));
+            if (masked && (MODE == 0 ? column < diagonal : column > diagonal)) p = 0.0f;
+            probability[mine] = p;
           }
-          p16[quad * 2] = pack_pair<T>(p[0], p[1]);
-          p16[quad * 2 + 1] = pack_pair<T>(p[2], p[3]);
-          g16[quad * 2] = pack_pair<T>(g[0], g[1]);
-          g16[quad * 2 + 1] = pack_pair<T>(g[2], g[3]);
+          p16[quad * 2] = pack_pair<T>(probability[chunk * 32 + quad * 4], probability[chunk * 32 + quad * 4 + 1]);
+          p16[quad * 2 + 1] = pack_pair<T>(probability[chunk * 32 + quad * 4 + 2], probability[chunk * 32 + quad * 4 + 3]);
         }
         // packed columns [64*half + 16*chunk, +16) lie over f32 columns this thread has already consumed
         if (MODE == 0) tc::tmem_store_32x16(tmem_t0 + lane_base + half * 64 + chunk * 16, p16);
+      }
+      if (MODE == 0) tc::tmem_store_wait();
+      tc::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&bars->p_ready);      // T0 has been read (and, MODE 0, holds P)
+      // phase B: G = P * (T1 - delta), 16 bits, back over T1
+      if (!tc::mbar_wait(&bars->t1_full, parity, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int chunk = 0; chunk < kTile / 64; ++chunk) {
+        uint32_t t1[32];
+        tc::tmem_load_32x32(tmem_t1 + lane_base + half * 64 + chunk * 32, t1);
+        tc::tmem_load_wait();
+        uint32_t g16[16];
+#pragma unroll
+        for (int quad = 0; quad < 8; ++quad) {
+          float d[4] = {row_delta, row_delta, row_delta, row_delta};
+          if (MODE == 0) {
+            const float4 d4 = *reinterpret_cast<const float4 *>(&bars->columns[compute_warp][1][chunk * 32 + quad * 4]);
+            d[0] = d4.x; d[1] = d4.y; d[2] = d4.z; d[3] = d4.w;
+          }
+          float g[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            g[e] = probability[chunk * 32 + quad * 4 + e] * (__uint_as_float(t1[quad * 4 + e]) - d[e]);
+          g16[quad * 2] = pack_pair<T>(g[0], g[1]);
+          g16[quad * 2 + 1] = pack_pair<T>(g[2], g[3]);
+        }
         tc::tmem_store_32x16(tmem_t1 + lane_base + half * 64 + chunk * 16, g16);
       }
       tc::tmem_store_wait();
