@@ -63,6 +63,13 @@ __device__ __forceinline__ float ex2_approx_ftz(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// A load the compiler may not sink to its first use: issued here, it is in flight while the
+// volatile statements that follow (barrier waits, TMEM traffic) run.
+__device__ __forceinline__ float load_now(const float *pointer) {
+  float value;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(value) : "l"(pointer));
+  return value;
+}
 template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
   __half2 v = __floats2half2_rn(lo, hi);
@@ -251,25 +258,47 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
       row_delta = delta[dat];
     }
     bool alive = true;
+    // MODE 0: the per-query lse and delta of a step are requested one step ahead (their global loads
+    // would otherwise sit in front of every step; nothing touches the loaded values until the next
+    // step parks them, scaled, in this warp's shared-memory copy)
+    float next_lse[kTile / 64], next_delta[kTile / 64];
+    // (head, first row) of the streamed tiles, stepped without divisions: `ahead` is one step in front
+    int now_head = MODE == 0 ? head * shape.head_group : head / shape.head_group, now_tile = first;
+    int ahead_head = now_head, ahead_tile = first;
+    auto advance = [&](int &h, int &t) {
+      if (++t == first + per_head) { t = first; ++h; }
+    };
+    auto request_columns = [&](int step) {
+#pragma unroll
+      for (int part = 0; part < kTile / 64; ++part) {
+        next_lse[part] = INFINITY;
+        next_delta[part] = 0.0f;
+        if (MODE == 0 && step < steps) {
+          const int query = ahead_tile * kTile + half * 64 + part * 32 + lane, hq = ahead_head;
+          if (query < shape.seq_q) {
+            next_lse[part] = load_now(lse + batch * shape.lse_stride[0] + hq * shape.lse_stride[1] + query * shape.lse_stride[2]);
+            next_delta[part] = load_now(delta + batch * shape.delta_stride[0] + hq * shape.delta_stride[1] + query * shape.delta_stride[2]);
+          }
+        }
+      }
+    };
+    request_columns(0);
+    advance(ahead_head, ahead_tile);
     for (int step = 0; alive && step < steps; ++step) {
       const int parity = step & 1;
-      const int streamed0 = y_row0(step);
+      const int streamed0 = now_tile * kTile;
+      advance(now_head, now_tile);
       if (MODE == 0) {
-        // this step's per-query lse*log2e and delta; every warp keeps its own copy, so no barrier
-        // between warps is needed (the previous step's reads ended at its __syncwarp)
-        const int hq = y_head(step);
+        // every warp keeps its own copy, so no barrier between warps is needed (the previous step's
+        // reads ended at its __syncwarp)
 #pragma unroll
         for (int part = 0; part < kTile / 64; ++part) {
-          const int query = streamed0 + half * 64 + part * 32 + lane;
-          float l = INFINITY, d = 0.0f;
-          if (query < shape.seq_q) {
-            l = lse[batch * shape.lse_stride[0] + hq * shape.lse_stride[1] + query * shape.lse_stride[2]] * kLog2e;
-            d = delta[batch * shape.delta_stride[0] + hq * shape.delta_stride[1] + query * shape.delta_stride[2]];
-          }
-          bars->columns[compute_warp][0][part * 32 + lane] = l;
-          bars->columns[compute_warp][1][part * 32 + lane] = d;
+          bars->columns[compute_warp][0][part * 32 + lane] = next_lse[part] * kLog2e;   // first use of the loaded value
+          bars->columns[compute_warp][1][part * 32 + lane] = next_delta[part];
         }
         __syncwarp();
+        request_columns(step + 1);
+        advance(ahead_head, ahead_tile);
       }
       // column c of the tile is excluded when its key lies after its query
       //   MODE 0: key = row, query = streamed0 + c  -> excluded when c < row - streamed0
