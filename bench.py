@@ -30,6 +30,7 @@ them under ``"ops"``.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import math
 import os
@@ -761,6 +762,8 @@ def main() -> None:
                 end_to_end = (steps + 2) if hasattr(case, "pipeline") else (1 + max(2, steps // 4))
                 launches += case.launches_per_step * (arguments.warmup + 3 * steps + end_to_end)
                 del case
+                gc.collect()
+                torch.cuda.empty_cache()   # every operator starts from fresh device allocations
             except Exception as error:  # one failing operator must not hide the others
                 if name == primary:
                     raise
