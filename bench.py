@@ -144,6 +144,23 @@ class Case:
         from intent_b200 import workloads
         self.device = device
         self.workloads = workloads
+        self._pipeline = None
+
+    @property
+    def pipeline(self):
+        """The end-to-end pipeline, built on first use: its device buffers and streams do not exist
+        while the device-resident figure is being measured."""
+        if self._pipeline is None:
+            self._pipeline = self.make_pipeline()
+        return self._pipeline
+
+    @property
+    def h2d(self):
+        return self.pipeline.h2d
+
+    @property
+    def d2h(self):
+        return self.pipeline.d2h
 
     def rotate(self, step: int):
         """Hook for cases whose working set is smaller than L2: pick a buffer set."""
@@ -235,8 +252,7 @@ class SoftmaxCase(Case):
         self.sets = [(self.host_x.to(device) + 0, torch.empty(4096, 1024, device=device)) for _ in range(12)]
         self.flush = "rotating 12 buffer pairs (384 MB > L2)"
         self.kernel = b200.jit(b200.kernels.stable_softmax)
-        self.pipeline = PipelinedEndToEnd(self.kernel, [self.host_x], (), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, [self.host_x], (), device)
 
     def launch(self, step):
         x, y = self.sets[step % len(self.sets)]
@@ -264,8 +280,7 @@ class LayerNormCase(Case):
         self.flush = "inputs larger than L2 (268 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.layer_norm_f16)
         # x travels every step; gamma and beta are parameters that stay on the device
-        self.pipeline = PipelinedEndToEnd(self.kernel, [x], (self.w, self.b, self.inv, self.eps), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, [x], (self.w, self.b, self.inv, self.eps), device)
 
     def launch(self, step):
         self.ops.layer_norm(self.x, self.w, self.b, self.inv, self.eps, out=self.y)
@@ -293,9 +308,8 @@ class GemmCase(Case):
         self.flush = "inputs larger than L2 (403 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.gemm, constexprs={"ACTIVATION": "NONE"})
         # B travels in its column-major storage (the transposed matrix is the contiguous one)
-        self.pipeline = PipelinedEndToEnd(self.kernel, [a, b.t().contiguous()], (), device,
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, [a, b.t().contiguous()], (), device,
                                           adapt=lambda buffers: (buffers[0], buffers[1].t()))
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
 
     def launch(self, step):
         self.ops.gemm(self.a, self.b, out=self.c)
@@ -324,8 +338,7 @@ class AttentionCase(Case):
         self.o = torch.empty_like(self.q)
         self.flush = "inputs larger than L2 (1074 MB per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.flash_attention_bf16_fwd, constexprs={"HEAD_GROUP": 1, "CAUSAL": True})
-        self.pipeline = PipelinedEndToEnd(self.kernel, [q, k, v], (self.scale,), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, [q, k, v], (self.scale,), device)
 
     def launch(self, step):
         self.ops.flash_attention(self.q, self.k, self.v, self.scale, out=self.o)
@@ -355,8 +368,7 @@ class SpmmCase(Case):
         self.y = torch.empty(262144, 128, device=device)
         self.flush = "inputs larger than L2 (337 MB compulsory per launch vs 126 MB)"
         self.kernel = b200.jit(b200.kernels.csr_spmm_262144)
-        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, list(self.host), (), device)
 
     def launch(self, step):
         self.ops.csr_spmm(*self.dev, out=self.y)
@@ -377,15 +389,17 @@ class SoftmaxBackwardCase(Case):
         from intent_b200 import ops
         self.ops, self.workload = ops, self.workloads.softmax_backward_workload()
         self.host = self.workloads.softmax_backward_inputs()
-        self.p, self.u = (t.to(device) for t in self.host)
-        self.g = torch.empty_like(self.p)
-        self.flush = "inputs larger than L2 (201 MB per launch vs 126 MB)"
+        # 201 MB per launch exceeds L2 (126 MB), but a good part of one working set would survive in it
+        # between launches: two sets alternate (403 MB), so every launch reads from DRAM
+        self.sets = [tuple(t.to(device) + 0 for t in self.host) + (torch.empty(4096, 4097, device=device),)
+                     for _ in range(2)]
+        self.flush = "alternating two copies of the operands (403 MB > L2)"
         self.kernel = b200.jit(b200.kernels.softmax_backward)
-        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, list(self.host), (), device)
 
     def launch(self, step):
-        self.ops.softmax_backward(self.p, self.u, out=self.g)
+        p, u, g = self.sets[step % 2]
+        self.ops.softmax_backward(p, u, out=g)
 
     def e2e(self, step):
         self.pipeline.step(step)
@@ -408,8 +422,7 @@ class SpmvCase(Case):
         self.sets = [[t.to(device) + 0 for t in self.host] + [torch.empty(32768, device=device)] for _ in range(20)]
         self.flush = "rotating 20 copies of the operands (172 MB > L2)"
         self.kernel = b200.jit(b200.kernels.csr_spmv)
-        self.pipeline = PipelinedEndToEnd(self.kernel, list(self.host), (), device)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(self.kernel, list(self.host), (), device)
 
     def launch(self, step):
         ro, ci, va, x, y = self.sets[step % len(self.sets)]
@@ -448,8 +461,7 @@ class LayerNormBackwardCase(Case):
             rows_call = self.rows.prepare(*buffers, self.inverse)
             reduce_call = self.reduce.prepare(buffers[5], buffers[6])
             return [rows_call, reduce_call], [rows_call.result(), *reduce_call.result()]
-        self.pipeline = PipelinedEndToEnd(None, list(self.host), (), device, build=build)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(None, list(self.host), (), device, build=build)
 
     def launch(self, step):
         *operands, dx = self.sets[step % len(self.sets)]
@@ -496,8 +508,7 @@ class AttentionBackwardCase(Case):
             common = (qd, kd, vd, gd, ld, delta_call.result(), self.scale)
             dkdv_call, dq_call = kernels[1].prepare(*common), kernels[2].prepare(*common)
             return [delta_call, dkdv_call, dq_call], [dq_call.result(), *dkdv_call.result()]
-        self.pipeline = PipelinedEndToEnd(None, list(self.host), (), device, build=build)
-        self.h2d, self.d2h = self.pipeline.h2d, self.pipeline.d2h
+        self.make_pipeline = lambda: PipelinedEndToEnd(None, list(self.host), (), device, build=build)
 
     def launch(self, step):
         q, k, v, output, grad_output, lse = self.dev
@@ -629,18 +640,16 @@ def cpu_baseline(case, workers: int) -> dict:
             "ms": milliseconds}
 
 
-def measure(case, steps: int, warmup: int, distributed: bool, world: int, peak_table: dict, peak_kind: str,
-            with_cpu: bool) -> dict:
+def measure_resident(case, steps: int, warmup: int, distributed: bool, world: int, peak_table: dict,
+                     peak_kind: str) -> dict:
+    """The device-resident figure and its roofline.  Every operator is measured this way before any
+    end-to-end pipeline (extra streams, pinned buffers, PCIe traffic) has run in the process."""
     workload = case.workload
     scale = 1e6 if workload.unit == "GB/s" else 1e9      # bytes/ms -> GB/s, flop/ms -> TFLOP/s
     first_window = len(CLOCKS.windows) if CLOCKS is not None else 0
     resident_ms = timed_graph(case.launch, steps, warmup, distributed, case.device)
     time.sleep(0.06)  # let the sampler deliver the sample that covers the end of the window
     own_clocks = CLOCKS.summary(CLOCKS.windows[first_window:]) if CLOCKS is not None else None
-    pipeline = getattr(case, "pipeline", None)
-    # a two-deep pipeline needs enough steps for its fill and drain not to dominate
-    e2e_ms = timed(case.e2e, steps if pipeline else max(2, steps // 4), 2 if pipeline else 1, distributed, case.device,
-                   begin=pipeline.begin if pipeline else None, finish=pipeline.finish if pipeline else None)
     per_gpu = workload.work / resident_ms / scale
     if workload.bound == "hbm":
         peak, peak_name = peak_table["hbm_gbs"], f"{peak_kind} STREAM-style copy"
@@ -648,17 +657,26 @@ def measure(case, steps: int, warmup: int, distributed: bool, world: int, peak_t
     else:  # timed after 0.25 s of the same load: the sustained cuBLAS figure is the like-for-like peak
         peak, peak_name = peak_table["bf16_tflops_sustained"], f"{peak_kind} cuBLAS bf16 sustained"
         burst = peak_table["bf16_tflops"]
-    result = {
+    return {
         "op": case.name, "workload": workload.description, "unit": workload.unit,
         "value": per_gpu * world, "ms_per_step": resident_ms,
-        "e2e": {"value": workload.work / e2e_ms / scale * world, "unit": workload.unit, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": case.h2d, "d2h_bytes_per_step": case.d2h},
         "roofline": {"bound": workload.bound, "achieved": per_gpu, "peak": peak, "unit": workload.unit,
                      "frac": per_gpu / peak, "peak_source": peak_name, "frac_of_burst_peak": per_gpu / burst,
                      "frac_of_nominal": per_gpu / NOMINAL[workload.bound],
                      "traffic": NCU_TRAFFIC_BYTES[case.name], "algorithmic": workload.work},
         "l2": case.flush, "clocks": own_clocks,
     }
+
+
+def measure_end_to_end(case, steps: int, distributed: bool, world: int, with_cpu: bool) -> dict:
+    """The same metric through the artifact API with host buffers, then the CPU sample."""
+    workload = case.workload
+    scale = 1e6 if workload.unit == "GB/s" else 1e9
+    pipeline = case.pipeline
+    # a two-deep pipeline needs enough steps for its fill and drain not to dominate
+    e2e_ms = timed(case.e2e, steps, 2, distributed, case.device, begin=pipeline.begin, finish=pipeline.finish)
+    result = {"e2e": {"value": workload.work / e2e_ms / scale * world, "unit": workload.unit, "ms_per_step": e2e_ms,
+                      "h2d_bytes_per_step": case.h2d, "d2h_bytes_per_step": case.d2h}}
     if with_cpu:
         import oracle
         result["cpu_baseline"] = cpu_baseline(case, oracle.default_workers())
@@ -751,23 +769,33 @@ def main() -> None:
     global CLOCKS
     with ClockSampler(local_rank) as clocks:
         CLOCKS = clocks
-        for name in names:
-            steps = arguments.steps
+        steps, cases = arguments.steps, {}
+        for name in names:               # pass 1: device-resident figures of every operator
             try:
-                case = CASES[name](device)
-                results[name] = measure(case, steps, arguments.warmup, distributed, world, peak_table, peak_kind,
-                                        with_cpu=(rank == 0 and world == 1))
-                # warm-up, the captured pass, the timed replay (the 0.25 s of load replays before it
-                # are not counted), then the end-to-end warm-up and steps
-                end_to_end = (steps + 2) if hasattr(case, "pipeline") else (1 + max(2, steps // 4))
-                launches += case.launches_per_step * (arguments.warmup + 3 * steps + end_to_end)
-                del case
-                gc.collect()
-                torch.cuda.empty_cache()   # every operator starts from fresh device allocations
+                cases[name] = CASES[name](device)
+                results[name] = measure_resident(cases[name], steps, arguments.warmup, distributed, world, peak_table,
+                                                 peak_kind)
             except Exception as error:  # one failing operator must not hide the others
                 if name == primary:
                     raise
+                cases.pop(name, None)
                 results[name] = {"op": name, "error": f"{type(error).__name__}: {error}"}
+        for name in names:               # pass 2: end to end through the artifact API, and the CPU sample
+            case = cases.pop(name, None)
+            if case is None:
+                continue
+            try:
+                results[name].update(measure_end_to_end(case, steps, distributed, world,
+                                                        with_cpu=(rank == 0 and world == 1)))
+                # warm-up, the captured pass, the timed replay (the 0.25 s of load replays before it
+                # are not counted), then the end-to-end warm-up and steps
+                launches += case.launches_per_step * (arguments.warmup + 3 * steps + steps + 2)
+            except Exception as error:
+                if name == primary:
+                    raise
+                results[name] = {"op": name, "error": f"{type(error).__name__}: {error}"}
+            del case
+            gc.collect()
             torch.cuda.empty_cache()
     clock_summary = clocks.summary()
     if distributed:
