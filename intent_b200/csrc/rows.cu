@@ -236,16 +236,32 @@ layer_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ weight,
     beta = staged + columns;
   }
 
-  for (int64_t row = (int64_t)blockIdx.x * kGroups + group; row < rows;
-       row += (int64_t)gridDim.x * kGroups) {
-    const T *source = x + row * x_pitch;
+  // the next row of this group is requested (raw, 128 bits per vector) before the current one is reduced
+  const int64_t row_step = (int64_t)gridDim.x * kGroups;
+  uint4 ahead[ITERS];
+  auto request = [&](int64_t row) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int column = (it * kRowThreads + lane_in_row) * kVec;
+      ahead[it] = make_uint4(0, 0, 0, 0);
+      if (row < rows && column < columns) ahead[it] = *reinterpret_cast<const uint4 *>(x + row * x_pitch + column);
+    }
+  };
+  request((int64_t)blockIdx.x * kGroups + group);
+  for (int64_t row = (int64_t)blockIdx.x * kGroups + group; row < rows; row += row_step) {
     float value[ITERS][kVec];
     float sum = 0.0f, squares = 0.0f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
+      const T *lanes = reinterpret_cast<const T *>(&ahead[it]);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) value[it][i] = Element<T>::widen(lanes[i]);
+    }
+    request(row + row_step);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
       const int column = (it * kRowThreads + lane_in_row) * kVec;
       if (column < columns) {
-        load_vector<T>(source + column, value[it]);
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
           sum += value[it][i];
