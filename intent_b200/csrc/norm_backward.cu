@@ -32,6 +32,13 @@ constexpr int kLanes = 8;           // CTAs per cluster = lanes of the update or
 // the value bf16(f32(a) + f32(b)) of the definition: the f32 sum of two bf16 numbers is exact unless
 // their exponents lie more than 16 apart, and then both roundings return the larger operand.
 __device__ __forceinline__ __nv_bfloat162 combine(__nv_bfloat162 a, __nv_bfloat162 b) { return __hadd2(a, b); }
+// A 128-bit load the compiler may not sink to its first use (the end of the kernel): issued here, it is
+// in flight while the rows are walked.
+__device__ __forceinline__ uint4 load_now(const void *pointer) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(pointer));
+  return v;
+}
 __device__ __forceinline__ float low_of(uint32_t pair) { return __uint_as_float(pair << 16); }
 __device__ __forceinline__ float high_of(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
 
@@ -61,6 +68,16 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
 #pragma unroll
     for (int i = 0; i < kVec / 2; ++i) dw[v][i] = db[v][i] = __floats2bfloat162_rn(0.0f, 0.0f);
     if (first + v * kRowStride < columns) w[v] = *reinterpret_cast<const uint4 *>(weight + first + v * kRowStride);
+  }
+  // CTA `lane` will combine its eighth of the columns at the end (N <= 8192: at most one vector per
+  // thread); the previous contents of those partial sums are requested now
+  const int vectors = columns / kVec, share = (vectors + kLanes - 1) / kLanes;
+  const int combine_index = lane * share + threadIdx.x;
+  const bool combines = threadIdx.x < share && combine_index < vectors;
+  uint4 old_sums[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  if (combines) {
+    old_sums[0] = load_now(dw_partial + group * dw_pitch + combine_index * kVec);
+    old_sums[1] = load_now(db_partial + group * db_pitch + combine_index * kVec);
   }
   // rows of this group: group + j * groups for j < count; this CTA takes j = lane, lane + 8, ...
   const int64_t count = rows > group ? (rows - group + groups - 1) / groups : 0;
@@ -144,10 +161,8 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
     *reinterpret_cast<uint4 *>(lane_sums + columns + column) = *reinterpret_cast<const uint4 *>(db[v]);
   }
   cluster.sync();
-  // CTA `lane` combines its eighth of the columns (in vectors of 8)
-  const int vectors = columns / kVec, share = (vectors + kLanes - 1) / kLanes;
-  for (int index = lane * share + threadIdx.x; index < min(vectors, (lane + 1) * share); index += kRowThreads) {
-    const int column = index * kVec;
+  if (combines) {
+    const int column = combine_index * kVec;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
       __nv_bfloat16 *destination = (which ? db_partial + group * db_pitch : dw_partial + group * dw_pitch) + column;
@@ -164,7 +179,7 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
 #pragma unroll
           for (int i = 0; i < kVec / 2; ++i) into[i] = combine(into[i], from[i]);
         }
-      uint4 old = *reinterpret_cast<const uint4 *>(destination);
+      uint4 old = old_sums[which];
       __nv_bfloat162 *result = reinterpret_cast<__nv_bfloat162 *>(&old);
       const __nv_bfloat162 *total = reinterpret_cast<const __nv_bfloat162 *>(&level[0]);
 #pragma unroll
