@@ -9,8 +9,9 @@
 //   the total is added to the element's previous contents.
 // A cluster of 8 CTAs owns one group and CTA l is lane l.  A CTA (8 warps) walks its lane's rows:
 // a thread owns 1, 2 or 4 vectors of 8 columns (N <= 2048, 4096, 8192), keeps the weight vector and its lane
-// sums in registers, requests the next row before it reduces the current one, forms the two row
-// sums (one barrier, double-buffered scratch) and writes dx with streaming stores.  The lane sums
+// sums in registers, keeps three rows of x and dy in flight towards a four-slot ring in shared memory
+// (asynchronous copies; each thread copies the vectors it reads, so no barrier guards the ring), forms
+// the two row sums (one barrier, double-buffered scratch) and writes dx with streaming stores.  The lane sums
 // then go to shared memory; after a cluster barrier CTA l reads the eight lanes' sums of its
 // eighth of the columns through distributed shared memory, combines them in the fixed tree, and
 // updates the partial-sum rows.  x and dy are read once, dx written once: no atomics, no scratch in
@@ -32,18 +33,34 @@ constexpr int kLanes = 8;           // CTAs per cluster = lanes of the update or
 // the value bf16(f32(a) + f32(b)) of the definition: the f32 sum of two bf16 numbers is exact unless
 // their exponents lie more than 16 apart, and then both roundings return the larger operand.
 __device__ __forceinline__ __nv_bfloat162 combine(__nv_bfloat162 a, __nv_bfloat162 b) { return __hadd2(a, b); }
-// A 128-bit load the compiler may not sink to its first use (the end of the kernel): issued here, it is
-// in flight while the rows are walked.
-__device__ __forceinline__ uint4 load_now(const void *pointer) {
-  uint4 v;
-  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(pointer));
-  return v;
+// Asynchronous copies global -> shared memory.  A thread only ever reads what it copied itself (or,
+// for the row statistics, what a lane of its own warp copied), so completion needs no mbarrier and
+// no spin: `wait_group` blocks the thread until its own groups have landed.
+__device__ __forceinline__ void copy_async_16(void *shared, const void *global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(shared)), "l"(global)
+               : "memory");
 }
+__device__ __forceinline__ void copy_async_4(void *shared, const void *global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(shared)), "l"(global)
+               : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+// The cluster barrier in two halves.  The releasing arrival waits for the thread's earlier writes (its
+// streaming stores of dx among them) to be performed, so it is issued before the last row's dx is
+// written; the relaxed form orders execution only.
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+constexpr int kRing = 3;            // rows of x and dy a CTA keeps in flight or in use
+
 __device__ __forceinline__ float low_of(uint32_t pair) { return __uint_as_float(pair << 16); }
 __device__ __forceinline__ float high_of(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
 
 template <int kRowThreads, int VECTORS>
-__global__ void __cluster_dims__(kLanes, 1, 1) __launch_bounds__(kRowThreads, VECTORS > 2 ? 1 : 2)
+__global__ void __cluster_dims__(kLanes, 1, 1) __launch_bounds__(kRowThreads, VECTORS > 2 ? 1 : 3)
 layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ dy,
                                 const __nv_bfloat16 *__restrict__ weight, const float *__restrict__ mean,
                                 const float *__restrict__ rstd, __nv_bfloat16 *__restrict__ dx,
@@ -52,7 +69,7 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
                                 int64_t dx_pitch, int64_t dw_pitch, int64_t db_pitch, int64_t mean_stride,
                                 int64_t rstd_stride, float inverse_features) {
   constexpr int kRowStride = kRowThreads * kVec;   // columns between a thread's vectors
-  extern __shared__ __align__(16) __nv_bfloat16 lane_sums[];  // [dw | db][columns]
+  extern __shared__ __align__(16) __nv_bfloat16 lane_sums[];  // [dw | db][columns], then the ring of rows
   __shared__ float scratch[2][kRowThreads / 32][2];
   cg::cluster_group cluster = cg::this_cluster();
   const int lane = (int)cluster.block_rank();
@@ -74,36 +91,71 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
   const int vectors = columns / kVec, share = (vectors + kLanes - 1) / kLanes;
   const int combine_index = lane * share + threadIdx.x;
   const bool combines = threadIdx.x < share && combine_index < vectors;
-  uint4 old_sums[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  __shared__ uint4 previous[2][128];                             // N <= 8192: a CTA combines at most 128 vectors
   if (combines) {
-    old_sums[0] = load_now(dw_partial + group * dw_pitch + combine_index * kVec);
-    old_sums[1] = load_now(db_partial + group * db_pitch + combine_index * kVec);
+    copy_async_16(&previous[0][threadIdx.x], dw_partial + group * dw_pitch + combine_index * kVec);
+    copy_async_16(&previous[1][threadIdx.x], db_partial + group * db_pitch + combine_index * kVec);
   }
   // rows of this group: group + j * groups for j < count; this CTA takes j = lane, lane + 8, ...
   const int64_t count = rows > group ? (rows - group + groups - 1) / groups : 0;
   const int64_t mine = count > lane ? (count - lane + kLanes - 1) / kLanes : 0;
-  uint4 x_next[VECTORS], dy_next[VECTORS];
-  float mean_next = 0.0f, rstd_next = 0.0f;
+  // Rows travel through a ring of kRing slots in shared memory: kRing - 1 rows are requested ahead
+  // of the one in use.  A thread copies exactly the vectors it will read; lane 0 of a warp copies the
+  // row's mean and rstd for its warp.  One group is committed per step, empty past the last row.
+  __nv_bfloat16 *ring = lane_sums + 2 * columns;                 // [kRing][x | dy][columns]
+  __shared__ float statistics[kRing][kRowThreads / 32][2];
   auto request = [&](int64_t step) {
-    const int64_t row = group + (lane + step * kLanes) * (int64_t)groups;
+    if (step < mine) {
+      const int64_t row = group + (lane + step * kLanes) * (int64_t)groups;
+      __nv_bfloat16 *slot = ring + (size_t)(step % kRing) * 2 * columns;
 #pragma unroll
-    for (int v = 0; v < VECTORS; ++v) {
-      x_next[v] = dy_next[v] = make_uint4(0, 0, 0, 0);
-      if (step < mine && first + v * kRowStride < columns) {
-        x_next[v] = __ldcs(reinterpret_cast<const uint4 *>(x + row * x_pitch + first + v * kRowStride));
-        dy_next[v] = __ldcs(reinterpret_cast<const uint4 *>(dy + row * dy_pitch + first + v * kRowStride));
+      for (int v = 0; v < VECTORS; ++v) {
+        const int column = first + v * kRowStride;
+        if (column < columns) {
+          copy_async_16(slot + column, x + row * x_pitch + column);
+          copy_async_16(slot + columns + column, dy + row * dy_pitch + column);
+        }
+      }
+      if (thread_lane == 0) {
+        copy_async_4(&statistics[step % kRing][warp][0], mean + row * mean_stride);
+        copy_async_4(&statistics[step % kRing][warp][1], rstd + row * rstd_stride);
       }
     }
-    if (step < mine) { mean_next = mean[row * mean_stride]; rstd_next = rstd[row * rstd_stride]; }
+    copy_async_commit();
   };
-  request(0);
+#pragma unroll
+  for (int ahead = 0; ahead < kRing - 1; ++ahead) request(ahead);
+  // this lane's sums, for the whole cluster to read: final once the last row has been added, which is
+  // before that row's dx is formed
+  auto publish = [&]() {
+#pragma unroll
+    for (int v = 0; v < VECTORS; ++v) {
+      const int column = first + v * kRowStride;
+      if (column >= columns) continue;
+      *reinterpret_cast<uint4 *>(lane_sums + column) = *reinterpret_cast<const uint4 *>(dw[v]);
+      *reinterpret_cast<uint4 *>(lane_sums + columns + column) = *reinterpret_cast<const uint4 *>(db[v]);
+    }
+    cluster_arrive_release();
+  };
+  if (mine == 0) publish();
   for (int64_t step = 0; step < mine; ++step) {
     const int64_t row = group + (lane + step * kLanes) * (int64_t)groups;
-    const float row_mean = mean_next, row_rstd = rstd_next;
+    // the slot of row step - 1 is free: every thread finished with it before the barrier of that step
+    request(step + kRing - 1);
+    copy_async_wait<kRing - 1>();
+    __syncwarp();                                                 // lane 0's copy of the statistics, for the warp
+    const __nv_bfloat16 *current = ring + (size_t)(step % kRing) * 2 * columns;
+    const float row_mean = statistics[step % kRing][warp][0], row_rstd = statistics[step % kRing][warp][1];
     uint4 x_raw[VECTORS], dy_raw[VECTORS];
 #pragma unroll
-    for (int v = 0; v < VECTORS; ++v) { x_raw[v] = x_next[v]; dy_raw[v] = dy_next[v]; }
-    request(step + 1);
+    for (int v = 0; v < VECTORS; ++v) {
+      const int column = first + v * kRowStride;
+      x_raw[v] = dy_raw[v] = make_uint4(0, 0, 0, 0);
+      if (column < columns) {
+        x_raw[v] = *reinterpret_cast<const uint4 *>(current + column);
+        dy_raw[v] = *reinterpret_cast<const uint4 *>(current + columns + column);
+      }
+    }
     float sum = 0.0f, sum_normalized = 0.0f;
 #pragma unroll
     for (int v = 0; v < VECTORS; ++v) {
@@ -128,6 +180,7 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
     float (*slot)[2] = scratch[step & 1];
     if (thread_lane == 0) { slot[warp][0] = sum; slot[warp][1] = sum_normalized; }
     __syncthreads();   // the other parity's slots are free again once every thread is past this point
+    if (step == mine - 1) publish();
     float total = 0.0f, total_normalized = 0.0f;
 #pragma unroll
     for (int other = 0; other < kRowThreads / 32; ++other) { total += slot[other][0]; total_normalized += slot[other][1]; }
@@ -136,8 +189,11 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
 #pragma unroll
     for (int v = 0; v < VECTORS; ++v) {
       if (first + v * kRowStride >= columns) continue;
-      const uint32_t *x_pairs = reinterpret_cast<const uint32_t *>(&x_raw[v]);
-      const uint32_t *dy_pairs = reinterpret_cast<const uint32_t *>(&dy_raw[v]);
+      // read again from the ring rather than held across the barrier (registers)
+      const uint4 x_again = *reinterpret_cast<const uint4 *>(current + first + v * kRowStride);
+      const uint4 dy_again = *reinterpret_cast<const uint4 *>(current + columns + first + v * kRowStride);
+      const uint32_t *x_pairs = reinterpret_cast<const uint32_t *>(&x_again);
+      const uint32_t *dy_pairs = reinterpret_cast<const uint32_t *>(&dy_again);
       const uint32_t *w_pairs = reinterpret_cast<const uint32_t *>(&w[v]);
       uint4 raw;
       __nv_bfloat162 *pairs = reinterpret_cast<__nv_bfloat162 *>(&raw);
@@ -152,15 +208,8 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
       __stcs(reinterpret_cast<uint4 *>(dx + row * dx_pitch + first + v * kRowStride), raw);
     }
   }
-  // this lane's sums, for the whole cluster to read
-#pragma unroll
-  for (int v = 0; v < VECTORS; ++v) {
-    const int column = first + v * kRowStride;
-    if (column >= columns) continue;
-    *reinterpret_cast<uint4 *>(lane_sums + column) = *reinterpret_cast<const uint4 *>(dw[v]);
-    *reinterpret_cast<uint4 *>(lane_sums + columns + column) = *reinterpret_cast<const uint4 *>(db[v]);
-  }
-  cluster.sync();
+  copy_async_wait<0>();                                          // the previous partial sums (own copies)
+  cluster_wait_acquire();
   if (combines) {
     const int column = combine_index * kVec;
 #pragma unroll
@@ -179,7 +228,7 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
 #pragma unroll
           for (int i = 0; i < kVec / 2; ++i) into[i] = combine(into[i], from[i]);
         }
-      uint4 old = old_sums[which];
+      uint4 old = previous[which][threadIdx.x];
       __nv_bfloat162 *result = reinterpret_cast<__nv_bfloat162 *>(&old);
       const __nv_bfloat162 *total = reinterpret_cast<const __nv_bfloat162 *>(&level[0]);
 #pragma unroll
@@ -187,7 +236,8 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
       *reinterpret_cast<uint4 *>(destination) = old;
     }
   }
-  cluster.sync();   // no CTA may leave while another still reads its shared memory
+  cluster_arrive_relaxed();   // no CTA may leave while another still reads its shared memory
+  cluster_wait_acquire();
 }
 
 // dw[n] = sum over groups (ascending) of f32(dw_partial[g, n]); likewise db.  A CTA owns 16 columns:
@@ -270,7 +320,7 @@ extern "C" int b200_layer_norm_backward_rows(
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "layer_norm_backward_rows: rows must be 16-byte aligned");
   if (dw_d0 > INT32_MAX / kLanes) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "layer_norm_backward_rows: too many groups");
   cudaStream_t queue = static_cast<cudaStream_t>(stream);
-  const size_t smem = 2 * (size_t)n * sizeof(__nv_bfloat16);
+  const size_t smem = (2 + 2 * kRing) * (size_t)n * sizeof(__nv_bfloat16);   // lane sums, then the ring
   auto launch = [&](auto kernel, int threads) -> cudaError_t {
     if (smem > 48 * 1024) {
       const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
