@@ -380,28 +380,50 @@ csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__
   if (active && touched) __stcs(reinterpret_cast<float4 *>(destination), acc);
 }
 
-// CSR SpMV  y = A . x  (csr_spmm with a single feature).  One warp per row: the 32
-// products of a batch are formed in parallel (separately rounded), then added to the
-// carry one by one in storage order, so the sum is the sequential left-to-right one.
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+// CSR SpMV  y = A . x  (csr_spmm with a single feature).  A warp takes kSpmvRows consecutive rows.
+// Batch by batch (32 stored elements of every row): the indices and values of all its rows are
+// requested before any is used, then all the gathers, and the products (separately rounded) are
+// staged in shared memory; then lane r adds row r's products to its carry one by one in storage
+// order, so every sum is the sequential left-to-right one and costs one shared-memory read and
+// one add per element for 16 rows at a time, not a shuffle per element per row.
+constexpr int kSpmvRows = 16, kSpmvWarps = 4;
+
+__global__ void __launch_bounds__(kSpmvWarps * 32)
 csr_spmv_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
                 const float *__restrict__ values, const float *__restrict__ vector, float *__restrict__ output,
                 int64_t rows, int64_t vector_stride, int64_t output_stride) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
+  __shared__ float staged[kSpmvWarps][kSpmvRows][33];            // 33: lane r walks row r without bank conflicts
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * kSpmvWarps + warp) * kSpmvRows;
+  if (row0 >= rows) return;                                      // whole warps leave; no CTA barrier below
+  const int here = (int)min((int64_t)kSpmvRows, rows - row0);
+  const int offset = lane <= here ? __ldg(row_offsets + row0 + lane) : 0;
+  const int next_offset = __shfl_down_sync(0xffffffffu, offset, 1);
+  const int length = lane < here ? next_offset - offset : 0;      // of row `lane`
+  int longest = length;
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, step));
   float acc = 0.0f;
-  for (int base = start; base < stop; base += 32) {
-    const int count = min(32, stop - base);
-    float product = 0.0f;
-    if (lane < count) {
-      const int column = __ldcs(column_indices + base + lane);
-      product = __fmul_rn(__ldcs(values + base + lane), __ldg(vector + (int64_t)column * vector_stride));
+  for (int base = 0; base < longest; base += 32) {
+    int column[kSpmvRows];
+    float value[kSpmvRows];
+#pragma unroll
+    for (int r = 0; r < kSpmvRows; ++r) {
+      const int at = __shfl_sync(0xffffffffu, offset, r) + base + lane, stop = __shfl_sync(0xffffffffu, offset, r + 1);
+      const bool stored = r < here && at < stop;
+      column[r] = stored ? __ldcs(column_indices + at) : -1;
+      value[r] = stored ? __ldcs(values + at) : 0.0f;
     }
-    for (int j = 0; j < count; ++j) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, product, j));
+#pragma unroll
+    for (int r = 0; r < kSpmvRows; ++r)
+      staged[warp][r][lane] = column[r] >= 0 ? __fmul_rn(value[r], __ldg(vector + (int64_t)column[r] * vector_stride)) : 0.0f;
+    __syncwarp();
+    const int count = min(32, length - base);                    // <= 0 once this lane's row is finished
+#pragma unroll 8
+    for (int j = 0; j < count; ++j) acc = __fadd_rn(acc, staged[warp][lane & (kSpmvRows - 1)][j]);
+    __syncwarp();
   }
-  if (lane == 0) output[row * output_stride] = acc;
+  if (lane < here) output[(row0 + lane) * output_stride] = acc;
 }
 
 // Number of column blocks: X is cut into slices of at most kBlockBytes so that a slice
@@ -556,9 +578,9 @@ extern "C" int b200_csr_spmv(const void *row_offsets, int64_t ro_d0, int64_t ro_
   if ((ro_d0 > 1 && ro_s0 != 1) || (ci_d0 > 1 && (ci_s0 != 1 || va_s0 != 1)))
     return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: index/value arrays must be contiguous");
   if (ci_d0 > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: i32 index space exceeded");
-  const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int64_t ctas = (rows + kSpmvWarps * kSpmvRows - 1) / (kSpmvWarps * kSpmvRows);
   if (ctas > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmv: too many rows");
-  csr_spmv_kernel<<<(unsigned)ctas, kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  csr_spmv_kernel<<<(unsigned)ctas, kSpmvWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values, (const float *)vector,
       (float *)output, rows, x_s0, y_s0);
   B200_CUDA_TRY(cudaGetLastError());

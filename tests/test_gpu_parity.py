@@ -217,6 +217,25 @@ def test_csr_spmv_bit_exact(rows, columns, per_row):
     assert torch.equal(ops.csr_spmv(*cuda(ro, ci, va), wide.to(DEV)[:, 1]).cpu(), y.cpu())
 
 
+@pytest.mark.parametrize("rows,longest", [(1003, 100), (7, 3), (130, 33)])
+def test_csr_spmv_ragged_rows(rows, longest):
+    """Row lengths from 0 to `longest` (empty rows, rows longer than one batch of 32), a row count
+    that is not a multiple of the rows a warp takes."""
+    g = torch.Generator().manual_seed(rows)
+    columns = 500
+    lengths = torch.randint(0, longest + 1, (rows,), generator=g)
+    lengths[::5] = 0
+    ro = torch.zeros(rows + 1, dtype=torch.int32)
+    ro[1:] = torch.cumsum(lengths, 0).to(torch.int32)
+    nnz = int(ro[-1])
+    ci = torch.cat([torch.sort(torch.randperm(columns, generator=g)[:int(n)]).values for n in lengths]
+                   + [torch.zeros(0, dtype=torch.int64)]).to(torch.int32)
+    va = torch.randn(nnz, generator=g)
+    vector = torch.randn(columns, generator=g)
+    y = ops.csr_spmv(*cuda(ro, ci, va, vector))
+    assert torch.equal(y.cpu(), oracle.csr_spmv(ro, ci, va, vector))
+
+
 @pytest.mark.parametrize("m,n", [(64, 4097), (7, 5), (130, 1024), (3, 30000)])
 def test_softmax_backward(m, n):
     g = torch.Generator().manual_seed(m + n)
