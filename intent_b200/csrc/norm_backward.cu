@@ -70,7 +70,11 @@ __device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.c
 constexpr int kRing = 4;            // rows of x and dy a CTA keeps in flight or in use
 
 // Both halves of a bf16 pair as f32; the arithmetic below works on such pairs with the packed f32x2
-// instructions (round-to-nearest per half, the same values as the scalar operations).
+// instructions.  Each rounds to nearest per half like its scalar form, with one caveat measured on
+// B200: a packed product that feeds a packed sum is contracted into one packed fma by the assembler,
+// explicit rounding modifiers or not.  The values that must match the typed definition bit for bit
+// (xhat = (x - mean) * rstd, dy * xhat, and the bf16 sums) contain no product feeding a sum; the f32
+// row sums and dx, which are compared within a tolerance, may be contracted.
 __device__ __forceinline__ float2 widen(uint32_t pair) {
   return make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
 }
@@ -211,8 +215,8 @@ layer_norm_backward_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_
         const uint32_t *dy_pairs = reinterpret_cast<const uint32_t *>(&dy_raw[v]);
 #pragma unroll
         for (int i = 0; i < kVec / 2; ++i) {
-          // xhat = (x - mean) * rstd and dy * xhat are formed unfused, in the reference's order, so the
-          // lane sums do not depend on contraction
+          // xhat = (x - mean) * rstd and dy * xhat: a sum feeding a product, and a bare product, so
+          // nothing here can be contracted and the lane sums are those of the typed definition
           const float2 d = widen(dy_pairs[i]);
           const float2 n = __fmul2_rn(__fadd2_rn(widen(x_pairs[i]), minus_mean), rstd_pair);
           const float2 g = __fmul2_rn(weight_pair(v, i), d);
