@@ -252,7 +252,7 @@ def test_softmax_backward(m, n):
 
 
 @pytest.mark.parametrize("m,n,groups", [(256, 512, 128), (130, 4096, 128), (77, 8192, 16), (5, 40, 3), (300, 1000, 128),
-                                         (2100, 2048, 300), (1000, 4096, 7), (700, 8192, 40)])
+                                         (2100, 2048, 300), (1000, 4096, 7), (700, 8192, 40), (3, 64, 8), (40, 128, 600)])
 def test_layer_norm_backward(m, n, groups):
     x, dy, w, mean, rstd, dw_partial, db_partial, inv = workloads.layer_norm_backward_inputs(m, n, groups, seed=m + n)
     # InOut: start from non-zero partial sums
