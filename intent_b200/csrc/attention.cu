@@ -242,8 +242,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       };
       auto release_slot = [&](int index) { tc::mma_commit(&bars->slot_empty[RingPosition(index).slot]); };
 
+      // Tile A's chain P_A(j) -> P.V_A(j) -> S_A(j+1) is the critical one: K_(j+1) and V_j are waited for
+      // while softmax A(j) still runs, so that S_A(j+1) is queued right behind P.V_A(j).
+      alive = alive && wait_slot(0);                                    // K_0
       for (int j = 0; alive && j < key_tiles; ++j) {
-        if (!wait_slot(2 * j)) break;                                   // K_j
         if (j < tiles_of[0]) issue_scores(0, j);
         if (j >= 1) {                                                   // P.V_B(j-1): covers softmax A(j)
           if (!wait_slot(2 * j - 1) || !issue_values(1, j - 1)) { alive = false; break; }
@@ -251,6 +253,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         issue_scores(1, j);                                             // tile B sees every key tile
         release_slot(2 * j);                                            // K_j
+        if (j + 1 < key_tiles && !wait_slot(2 * j + 2)) { alive = false; break; }   // K_(j+1)
         if (j < tiles_of[0]) {                                          // P.V_A(j): covers softmax B(j)
           if (!wait_slot(2 * j + 1) || !issue_values(0, j)) { alive = false; break; }
         }
