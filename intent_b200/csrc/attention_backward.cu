@@ -228,14 +228,35 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
           if (!tc::mbar_wait(&bars->p_ready, step & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
           tc::tc_fence_after_sync();
           if (MODE == 0) issue_gradient(tmem_acc0, tmem_t0, 1, step);
-          if (more) {
-            if (!wait_stage(step + 1)) break;
-            issue_scores(0, step + 1);
+          // S(i+1) needs the next streamed tiles, acc1 += G.Y0 needs G(i): whichever is ready first is
+          // issued first.  With a two-stage ring the next tiles are requested only once this step's
+          // gradient product has released its stage, so issuing that product without waiting for the
+          // tiles of step i+1 gives their copy a head start.
+          bool scores_issued = !more, gradient_issued = false;
+          const long long waiting_since = clock64();
+          uint32_t spins = 0;
+          while (!(scores_issued && gradient_issued)) {
+            if (!scores_issued &&
+                tc::mbar_try_wait(&bars->y_full[(step + 1) % kStages], ((step + 1) / kStages) & 1)) {
+              tc::tc_fence_after_sync();
+              issue_scores(0, step + 1);
+              scores_issued = true;
+            } else if (!gradient_issued && tc::mbar_try_wait(&bars->g_ready, step & 1)) {
+              tc::tc_fence_after_sync();
+              issue_gradient(tmem_acc1, tmem_t1, 0, step);
+              tc::mma_commit(&bars->y_empty[step % kStages]);  // both gradient products of the step have read its tiles
+              gradient_issued = true;
+            } else if ((++spins & 0x3ffu) == 0) {
+              if (*abort_flag) break;
+              if (clock64() - waiting_since > tc::kWaitCycles) {
+                *abort_flag = 1;
+                if (atomicCAS(status, 0, 1) == 0) status[1] = tc::kSiteMmaTmemEmpty;
+                __threadfence();
+                break;
+              }
+            }
           }
-          if (!tc::mbar_wait(&bars->g_ready, step & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) break;
-          tc::tc_fence_after_sync();
-          issue_gradient(tmem_acc1, tmem_t1, 0, step);
-          tc::mma_commit(&bars->y_empty[step % kStages]);      // both gradient products of the step have read its tiles
+          if (!(scores_issued && gradient_issued)) break;
           if (more) issue_scores(1, step + 1);
           else tc::mma_commit(&bars->acc_full);
         }
