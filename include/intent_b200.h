@@ -278,12 +278,24 @@ int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2
  * Indices are trusted as the kernel's assume_in_bounds states
  * (csr_spmm.py:26-29); b200_csr_validate checks them on the device.
  * Requires contiguous index/value arrays and unit inner strides of X and Y.
+ * row_offsets may be a block of a longer offsets array (absolute offsets into
+ * column_indices / values): row r covers non-zeros [row_offsets[r], row_offsets[r+1]).
+ *
+ * The workspace is invocation-owned like the reference's native workspaces
+ * (python/intent/runtime/native.py:207-209): B200_WORKSPACE_WORDS int32 words,
+ * zeroed once by the caller.  Words 0-1 are the timeout report read by
+ * b200_csr_spmm_status; word 2 carries, from the first launch of a call to its
+ * later ones, whether every row ascends (a call on an X larger than L2 runs as
+ * several launches over column blocks, and falls back to one pass in storage
+ * order when a row does not ascend).  All state of a call lives in its
+ * workspace: calls with distinct workspaces may overlap on different streams.
  */
 int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
                   const void *column_indices, int64_t ci_d0, int64_t ci_s0,
                   const void *values, int64_t va_d0, int64_t va_s0,
                   const void *dense, int64_t x_d0, int64_t x_d1, int64_t x_s0, int64_t x_s1,
                   void *output, int64_t y_d0, int64_t y_d1, int64_t y_s0, int64_t y_s1,
+                  void *workspace, int64_t ws_d0, int64_t ws_s0,
                   void *stream);
 
 /*
@@ -310,12 +322,25 @@ int b200_csr_validate(const void *row_offsets, int64_t rows, const void *column_
 
 /*
  * b200_csr_spmm waits for its staged gathers with a bound.  If such a wait
- * ever gave up, the affected row was left unwritten and a device-side flag was
- * raised; this call synchronises `stream`, returns B200_ERR_DEVICE_TIMEOUT
- * (clearing the flag) and stores the row in *row (may be null), else B200_OK.
- * No counterpart in the reference.
+ * ever gave up, the affected row was left unwritten and words 0-1 of the
+ * call's workspace were set; this call synchronises `stream`, returns
+ * B200_ERR_DEVICE_TIMEOUT (clearing the words) and stores the row in *row
+ * (may be null), else B200_OK.  No counterpart in the reference.
  */
-int b200_csr_spmm_status(int64_t *row, void *stream);
+int b200_csr_spmm_status(const void *workspace, int64_t *row, void *stream);
+
+/*
+ * Measures what bounds the SpMM gathers on this device: `gathers` reads of
+ * 512-byte rows at pseudo-random positions of `table` (table_rows x 128 f32).
+ * variant 0..3: 4, 8, 16, 32 loads in flight per lane (64 warps per SM);
+ * variant 4: staged through shared memory by the copy engine as b200_csr_spmm
+ * does.  hints != 0 asks L2 to keep the gathered lines.  `sink` (>= 1 MiB) is
+ * never written in practice; `workspace` as for b200_csr_spmm.  A measurement
+ * aid with no counterpart in the reference: bench.py times it to report the
+ * gather ceiling beside the SpMM figure.
+ */
+int b200_gather_probe(const void *table, int64_t table_rows, int64_t gathers, int32_t variant,
+                      int32_t hints, void *sink, void *workspace, void *stream);
 
 /*
  * Reads word 0 of a workspace after synchronising `stream`: B200_OK, or

@@ -18,14 +18,15 @@ from __future__ import annotations
 
 import os
 
-from . import _native, ops
+from . import _native, ops, sharding
 from .compilation import (COMPILER, CompilationStageError, CompileOptions, GeneratedProgram, JITKernel,
                   device_capabilities, generate, jit, kernels)
+from .host_buffers import HostBuffers
 from .runtime import Artifact, B200Call, B200Program, Interface, PreparedSequence, register_operator
 
 __all__ = ["register", "jit", "generate", "kernels", "COMPILER", "CompileOptions", "GeneratedProgram",
            "JITKernel", "Artifact", "PreparedSequence", "B200Program", "B200Call", "Interface", "CompilationStageError",
-           "device_capabilities", "register_operator", "ops"]
+           "device_capabilities", "register_operator", "ops", "sharding", "HostBuffers"]
 
 
 def register(*, set_compiler: bool = True) -> None:

@@ -37,7 +37,7 @@ SIGNATURES = {
     "b200_gemm": _view(2) + _view(2) + _view(2) + _view(1) + [_I32, _I32, _P],
     "b200_gemm_static_scratch": _view(2) + _view(2) + _view(2) + [_I32, _I32, _I32, _P],
     "b200_flash_attention": _view(4) * 4 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
-    "b200_csr_spmm": _view(1) * 3 + _view(2) * 2 + [_P],
+    "b200_csr_spmm": _view(1) * 3 + _view(2) * 2 + _view(1) + [_P],
     "b200_csr_spmv": _view(1) * 5 + [_P],
     "b200_softmax_backward": _view(2) * 3 + [_I32, _P],
     "b200_layer_norm_backward_rows": _view(2) * 2 + _view(1) * 3 + _view(2) * 3 + [_F32, _P],
@@ -46,7 +46,8 @@ SIGNATURES = {
     "b200_attention_backward_dkdv": _view(4) * 4 + _view(3) * 2 + _view(4) * 2 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_attention_backward_dq": _view(4) * 4 + _view(3) * 2 + _view(4) + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
-    "b200_csr_spmm_status": [ctypes.POINTER(_I64), _P],
+    "b200_csr_spmm_status": [_P, ctypes.POINTER(_I64), _P],
+    "b200_gather_probe": [_P, _I64, _I64, _I32, _I32, _P, _P, _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],
     "b200_device_check": [ctypes.c_int],
     "b200_device_capabilities": [ctypes.c_int, ctypes.POINTER(_I64)],

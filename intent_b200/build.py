@@ -89,9 +89,43 @@ def build_compiler(*, force: bool = False) -> Path:
     return COMPILER
 
 
+REFERENCE_INSTALL = ROOT / "baseline" / "_ref"
+
+
+def reference_checkout() -> Path | None:
+    """The reference checkout, when this machine has one: named by INTENT_REFERENCE, else a
+    ``reference`` directory beside this repository."""
+    candidate = Path(os.environ.get("INTENT_REFERENCE", ROOT.parent / "reference"))
+    return candidate if (candidate / "python" / "intent" / "__init__.py").is_file() else None
+
+
+def install_reference() -> Path | None:
+    """Installs the reference's pure-Python package (and its example scripts) from the
+    checkout into ``baseline/_ref``, which is kept out of version control.  The provider is
+    tested through the unmodified reference from there on machines without the checkout.
+    (``pip install`` of the checkout is not possible offline: its build backend needs
+    setuptools-scm and the LLVM/MLIR 20 SDK; the Python package itself needs neither.)"""
+    checkout = reference_checkout()
+    if checkout is None:
+        return REFERENCE_INSTALL if (REFERENCE_INSTALL / "intent" / "__init__.py").is_file() else None
+    stamp = REFERENCE_INSTALL / ".installed-from"
+    newest = max(path.stat().st_mtime for path in (checkout / "python" / "intent").rglob("*.py"))
+    if stamp.is_file() and stamp.stat().st_mtime >= newest and stamp.read_text() == str(checkout):
+        return REFERENCE_INSTALL
+    if REFERENCE_INSTALL.exists():
+        shutil.rmtree(REFERENCE_INSTALL)
+    ignore = shutil.ignore_patterns("__pycache__", "*.pyc")
+    shutil.copytree(checkout / "python" / "intent", REFERENCE_INSTALL / "intent", ignore=ignore)
+    if (checkout / "examples").is_dir():
+        shutil.copytree(checkout / "examples", REFERENCE_INSTALL / "examples", ignore=ignore)
+    stamp.write_text(str(checkout))
+    return REFERENCE_INSTALL
+
+
 def build_all(*, force: bool = False, verbose: bool = False) -> None:
     build_library(force=force, verbose=verbose)
     build_compiler(force=force)
+    install_reference()
 
 
 if __name__ == "__main__":

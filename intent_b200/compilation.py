@@ -245,7 +245,7 @@ class GeneratedProgram:
         except (OSError, ValueError, KeyError) as error:
             raise CompilationStageError("generated_program_loading", str(error), cache_directory=path) from error
 
-    def materialize(self, *, device: int = 0) -> Artifact:
+    def materialize(self, *, device: int = 0, gpus=None, gather_output: bool = False) -> Artifact:
         """Bind to a device; refuses a device whose facts differ from the compiled ones
         (python/intent/targets/nvidia/target.py:25-31)."""
         _native.check("b200_device_check", _native.entry("b200_device_check")(int(device)))
@@ -255,7 +255,8 @@ class GeneratedProgram:
                 "generated_source_materialization",
                 f"generated target {self.metadata['target']['capabilities']} does not match the selected "
                 f"runtime target {current}")
-        return Artifact(self.source, self.ir, device, B200Program(self.metadata, device))
+        return Artifact(self.source, self.ir, device,
+                        B200Program(self.metadata, device, gpus=gpus, gather_output=gather_output))
 
 
 _generated: dict[str, GeneratedProgram] = {}
@@ -279,98 +280,131 @@ def generate(definition: KernelDefinition, *, capabilities: dict | None = None, 
 
 
 # --------------------------------------------------------------------------- JIT
-class JITKernel:
-    """One definition, one artifact per device (python/intent/jit/kernel.py:14-125)."""
+_BACKEND_OPTIONS = frozenset({"gpus", "gather_output"})
 
-    def __init__(self, definition, *, backend, device=None, compiler=None, constexprs=None, options=None):
+
+def _cuda_ordinal(device) -> int | None:
+    if device is None:
+        return None
+    return device if isinstance(device, int) else torch.device(device).index
+
+
+def _ordinal_of_call(tensors, requested) -> int:
+    """The one CUDA ordinal a call runs on: every tensor argument must live there, and an
+    explicit ``device=`` must agree with them."""
+    seen = []
+    for tensor in tensors:
+        if not isinstance(tensor, torch.Tensor):
+            continue
+        if tensor.device.type != "cuda":
+            raise ValueError(f"backend 'b200' executes on cuda, but arguments select {tensor.device}")
+        if tensor.device.index not in seen:
+            seen.append(tensor.device.index)
+    if len(seen) > 1:
+        raise ValueError(f"JIT arguments span different devices: {sorted(seen)}")
+    chosen = _cuda_ordinal(requested)
+    if chosen is None:
+        if not seen:
+            raise ValueError("JIT requires a device-bearing input or an explicit local device")
+        return seen[0]
+    if seen and seen[0] != chosen:
+        raise ValueError(f"explicit device cuda:{chosen} conflicts with the input device cuda:{seen[0]}")
+    return chosen
+
+
+class JITKernel:
+    """A kernel definition plus the artifacts compiled from it, one per CUDA device, made on
+    first use.  Same surface as the reference's JIT object (``python/intent/jit/kernel.py``):
+    ``prepare`` / ``run`` / call with explicit outputs / ``as_torch_op`` / ``close``.
+
+    ``backend_options`` takes ``gpus`` (number of ranks, or their CUDA ordinals in rank order)
+    and ``gather_output``: one process per GPU makes the same call with the same full operands,
+    each computes its block of rows / M-tiles / (batch, head) units, and with ``gather_output``
+    one all-gather completes the output on every rank (``intent_b200.sharding``)."""
+
+    def __init__(self, definition, *, backend, device=None, compiler=None, constexprs=None, options=None,
+                 backend_options=None):
         if not isinstance(definition, KernelDefinition):
             raise TypeError("intent_b200.jit requires one of intent_b200.kernels.*")
         if backend != "b200":
             raise ValueError(f"Unknown backend {backend!r}; choose from b200")
+        unknown = set(backend_options or {}) - _BACKEND_OPTIONS
+        if unknown:
+            raise ValueError(f"unsupported local b200 options: {sorted(unknown)}")
         self.definition, self.backend, self.device = definition, backend, device
         self.compiler, self.options = compiler, options
         self.constexprs = dict(constexprs or {})
-        self._artifacts: dict[int, Artifact] = {}
-        self._lock = RLock()
-        self._closed = False
+        self.backend_options = dict(backend_options or {})
         self.__name__ = definition.name
+        self._guard = RLock()
+        self._per_device: dict[int, Artifact] | None = {}      # None once closed
 
+    # -- what has been compiled so far -----------------------------------------------
     @property
-    def artifacts(self):
-        with self._lock:
-            return tuple(self._artifacts.values())
+    def artifacts(self) -> tuple:
+        with self._guard:
+            return tuple((self._per_device or {}).values())
+
+    def _only_artifact(self, purpose: str) -> Artifact:
+        compiled = self.artifacts
+        if len(compiled) != 1:
+            raise ValueError(f"prepare one {purpose}")
+        return compiled[0]
 
     @property
     def interface(self):
-        artifacts = self.artifacts
-        if len(artifacts) != 1:
-            raise ValueError("prepare one local specialization before inspecting its interface")
-        return artifacts[0].interface
+        return self._only_artifact("local specialization before inspecting its interface").interface
 
-    def _select_device(self, arguments) -> int:
-        observed = set()
-        for value in arguments:
-            if isinstance(value, torch.Tensor):
-                if value.device.type != "cuda":
-                    raise ValueError(f"backend 'b200' executes on cuda, but arguments select {value.device}")
-                observed.add(value.device.index)
-        if len(observed) > 1:
-            raise ValueError(f"JIT arguments span different devices: {sorted(observed)}")
-        explicit = None
-        if self.device is not None:
-            explicit = self.device if isinstance(self.device, int) else torch.device(self.device).index
-        if explicit is None and not observed:
-            raise ValueError("JIT requires a device-bearing input or an explicit local device")
-        selected = explicit if explicit is not None else next(iter(observed))
-        if observed and selected != next(iter(observed)):
-            raise ValueError(f"explicit device cuda:{selected} conflicts with the input device cuda:{next(iter(observed))}")
-        return selected
+    def as_torch_op(self, name):
+        return self._only_artifact(
+            "device specialization before registering its PyTorch operator").as_torch_op(name)
 
-    def _artifact(self, arguments, outputs) -> Artifact:
-        device = self._select_device((*arguments, *(outputs or ())))
-        with self._lock:
-            if self._closed:
+    # -- compile on demand -----------------------------------------------------------
+    def _program(self, capabilities=None) -> GeneratedProgram:
+        return generate(self.definition, capabilities=capabilities, constexprs=self.constexprs,
+                        options=self.options, compiler=self.compiler)
+
+    def _artifact_for(self, tensors) -> Artifact:
+        ordinal = _ordinal_of_call(tensors, self.device)
+        with self._guard:
+            if self._per_device is None:
                 raise RuntimeError("JIT kernel is closed")
-            if device not in self._artifacts:
-                program = generate(self.definition, capabilities=device_capabilities(device),
-                                   constexprs=self.constexprs, options=self.options, compiler=self.compiler)
-                self._artifacts[device] = program.materialize(device=device)
-            return self._artifacts[device]
+            artifact = self._per_device.get(ordinal)
+            if artifact is None:
+                artifact = self._program(device_capabilities(ordinal)).materialize(device=ordinal,
+                                                                                   **self.backend_options)
+                self._per_device[ordinal] = artifact
+            return artifact
 
+    # -- calls -------------------------------------------------------------------------
     def prepare(self, *arguments, outputs=None):
         if outputs is not None and not isinstance(outputs, tuple):
             raise TypeError("outputs must be a tuple in declared Out order")
-        return self._artifact(arguments, outputs).prepare(*arguments, outputs=outputs)
+        artifact = self._artifact_for(arguments if outputs is None else (*arguments, *outputs))
+        return artifact.prepare(*arguments, outputs=outputs)
 
     def run(self, *arguments):
-        call = self.prepare(*arguments)
-        call.launch()
-        return call.result()
+        prepared = self.prepare(*arguments)
+        prepared.launch()
+        return prepared.result()
 
     def __call__(self, *arguments):
-        interface = generate(self.definition, constexprs=self.constexprs, options=self.options,
-                             compiler=self.compiler)
+        """All runtime parameters in declaration order, output buffers included."""
         from .runtime import Interface
-        parameters = Interface.read(interface.metadata["interface"]).parameters
-        if len(parameters) != len(arguments):
-            raise TypeError(f"expected {len(parameters)} runtime arguments, got {len(arguments)}")
-        inputs, outputs = [], []
-        for parameter, value in zip(parameters, arguments):
-            (outputs if isinstance(parameter, ViewParameter) and parameter.output else inputs).append(value)
-        self.prepare(*inputs, outputs=tuple(outputs)).launch()
+        declared = Interface.read(self._program().metadata["interface"]).parameters
+        if len(arguments) != len(declared):
+            raise TypeError(f"expected {len(declared)} runtime arguments, got {len(arguments)}")
+        is_output = [isinstance(parameter, ViewParameter) and parameter.output for parameter in declared]
+        supplied = tuple(value for value, out in zip(arguments, is_output) if not out)
+        buffers = tuple(value for value, out in zip(arguments, is_output) if out)
+        self.prepare(*supplied, outputs=buffers).launch()
 
-    def as_torch_op(self, name):
-        artifacts = self.artifacts
-        if len(artifacts) != 1:
-            raise ValueError("prepare one device specialization before registering its PyTorch operator")
-        return artifacts[0].as_torch_op(name)
-
+    # -- lifetime ------------------------------------------------------------------------
     def close(self):
-        with self._lock:
-            for artifact in self._artifacts.values():
+        with self._guard:
+            for artifact in (self._per_device or {}).values():
                 artifact.runtime.close()
-            self._artifacts.clear()
-            self._closed = True
+            self._per_device = None
 
     def __enter__(self):
         return self
@@ -379,6 +413,7 @@ class JITKernel:
         self.close()
 
 
-def jit(definition, *, backend="b200", device=None, compiler=None, constexprs=None, options=None):
+def jit(definition, *, backend="b200", device=None, compiler=None, constexprs=None, options=None,
+        backend_options=None):
     return JITKernel(definition, backend=backend, device=device, compiler=compiler,
-                     constexprs=constexprs, options=options)
+                     constexprs=constexprs, options=options, backend_options=backend_options)

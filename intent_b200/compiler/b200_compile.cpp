@@ -450,6 +450,7 @@ Plan classify(const std::vector<Parameter> &all, const std::vector<Operation> &o
               "the dense operand and the output must both be f32 vectors or both f32 matrices");
       plan.family = "csr_spmm";
       plan.entry = "b200_csr_spmm";
+      plan.workspace = true;   // per-call state: timeout report and the "rows ascend" word
     }
     plan.contiguous = {0, 1, 2};
     return plan;

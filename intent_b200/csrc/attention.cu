@@ -445,12 +445,7 @@ int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd,
   result = tensor_map_4d(&map_v, v, batch, heads_k, seq_k, kHeadDim, vs[0], vs[1], vs[2]);
   if (result != B200_OK) return result;
   auto kernel = attention_kernel<T, kHeadDim>;
-  static std::once_flag configured;
-  cudaError_t attribute_error = cudaSuccess;
-  std::call_once(configured, [&] {
-    attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-  });
-  B200_CUDA_TRY(attribute_error);
+  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, kSmemBytes));
   Shape shape;
   shape.batch = (int)batch; shape.heads_q = (int)heads_q; shape.seq_q = (int)seq_q; shape.seq_k = (int)seq_k;
   shape.head_group = head_group; shape.causal = causal;

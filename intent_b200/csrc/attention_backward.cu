@@ -535,12 +535,7 @@ int launch_backward(const View4 &q, const View4 &k, const View4 &v, const View4 
   if (result != B200_OK) return result;
   constexpr size_t smem = 1024 + (2 + 2 * L::kStages) * L::kTileBytes + sizeof(Barriers);
   auto kernel = attention_backward_kernel<T, kHeadDim, MODE>;
-  static std::once_flag configured;
-  static cudaError_t attribute_error = cudaSuccess;
-  std::call_once(configured, [&] {
-    attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  });
-  B200_CUDA_TRY(attribute_error);
+  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, smem));
   Shape shape;
   shape.heads_q = (int)q.extents[1]; shape.heads_k = (int)k.extents[1];
   shape.seq_q = (int)q.extents[2]; shape.seq_k = (int)k.extents[2];

@@ -14,6 +14,13 @@ namespace b200 {
 int fail(int status, const char *format, ...);
 int cuda_fail(cudaError_t error, const char *what);
 int sm_count();  // multiprocessors of the current device (cached per device)
+// Opts `kernel` into `bytes` of dynamic shared memory on the CURRENT device.  The attribute is
+// per device and per function, so the answer is remembered per (function, device); an error is
+// returned on every call that meets it, not only on the first.
+cudaError_t opt_in_dynamic_smem(const void *kernel, size_t bytes);
+template <typename Kernel> cudaError_t opt_in_dynamic_smem(Kernel kernel, size_t bytes) {
+  return opt_in_dynamic_smem(reinterpret_cast<const void *>(kernel), bytes);
+}
 
 #define B200_CUDA_TRY(expression)                                   \
   do {                                                              \

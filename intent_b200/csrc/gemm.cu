@@ -315,12 +315,7 @@ int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, in
   if (result != B200_OK) return result;
   auto kernel = b_n_major ? (relu ? gemm_kernel<T, true, true> : gemm_kernel<T, false, true>)
                           : (relu ? gemm_kernel<T, true, false> : gemm_kernel<T, false, false>);
-  static std::once_flag configured[8];
-  cudaError_t attribute_error = cudaSuccess;
-  std::call_once(configured[(std::is_same<T, __half>::value ? 0 : 4) + (relu ? 1 : 0) + (b_n_major ? 2 : 0)], [&] {
-    attribute_error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-  });
-  B200_CUDA_TRY(attribute_error);
+  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, kSmemBytes));
   const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + kBlockN - 1) / kBlockN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, c, c_pitch, (int)m, (int)n, (int)k, status);

@@ -467,9 +467,7 @@ int launch_layer_norm_rows(const T *x, const T *w, const T *b, T *y, int64_t row
   const size_t parameter_bytes = 2 * (size_t)columns * sizeof(T);
   const int stage = parameter_bytes <= (size_t)kMaxStagedParameterBytes;
   const size_t smem = stage ? parameter_bytes : 0;
-  if (smem > 48 * 1024)
-    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kMaxStagedParameterBytes));
+  if (smem > 48 * 1024) B200_CUDA_TRY(opt_in_dynamic_smem(kernel, kMaxStagedParameterBytes));
   const int grid = grid_for(rows, Shape::kGroups, resident_ctas(kernel, Shape::kCtaThreads, smem));
   kernel<<<grid, Shape::kCtaThreads, smem, stream>>>(x, w, b, y, rows, (int)columns, xp, yp,
                                                      inverse_features, epsilon, stage);
@@ -603,14 +601,7 @@ extern "C" int b200_softmax_backward(const void *p, int64_t p_d0, int64_t p_d1, 
   const size_t row_bytes = 2 * (size_t)p_d1 * sizeof(float);
   const int staged = row_bytes <= 96 * 1024;
   const size_t smem = staged ? row_bytes : 0;
-  if (smem > 48 * 1024) {
-    static std::once_flag configured;
-    static cudaError_t attribute_error = cudaSuccess;
-    std::call_once(configured, [] {
-      attribute_error = cudaFuncSetAttribute(softmax_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    });
-    B200_CUDA_TRY(attribute_error);
-  }
+  if (smem > 48 * 1024) B200_CUDA_TRY(opt_in_dynamic_smem(softmax_backward_kernel, 96 * 1024));
   const int resident = resident_ctas(softmax_backward_kernel, 256, smem);
   const int64_t wanted = p_d0, limit = (int64_t)sm_count() * resident;
   softmax_backward_kernel<<<(unsigned)(wanted < limit ? wanted : limit), 256, smem, static_cast<cudaStream_t>(stream)>>>(

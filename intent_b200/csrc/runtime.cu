@@ -4,6 +4,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -22,6 +26,20 @@ int cuda_fail(cudaError_t error, const char *what) {
   snprintf(last_error, sizeof last_error, "%s: %s (%s)", what, cudaGetErrorString(error),
            cudaGetErrorName(error));
   return B200_ERR_CUDA;
+}
+
+cudaError_t opt_in_dynamic_smem(const void *kernel, size_t bytes) {
+  static std::mutex lock;
+  static std::map<std::pair<const void *, int>, size_t> granted;
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return error;
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = granted.find({kernel, device});
+  if (found != granted.end() && found->second >= bytes) return cudaSuccess;
+  error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (error == cudaSuccess) granted[{kernel, device}] = bytes;
+  return error;
 }
 
 int sm_count() {

@@ -1,0 +1,211 @@
+"""An explicit transfer scope for calls whose operands live in host memory.
+
+Binding never moves data: a prepared b200 call takes CUDA tensors only, exactly as the
+reference's JIT "never moves inputs implicitly".  A caller that holds NumPy arrays or CPU
+tensors asks for the transfers here, the way the reference's ``HostBuffers`` does for its
+example programs (``python/intent/runtime/host_buffers.py:53-149``): ``input`` stages a host
+allocation on the device and returns the device view to bind, ``finish`` brings writable
+storage and registered results back, ``reset`` restores preserved inputs, ``close`` releases
+everything.  With the reference installed its own class runs over b200 calls unchanged (the
+provider's ``host_storage`` is the reference's ``TorchStorage``); this class serves the
+stand-alone door and adds what a throughput caller on this hardware needs:
+
+* host allocations are page-locked in place (``cudaHostRegister``) so copies are asynchronous
+  DMA straight from and to the caller's memory, with no pinned staging copy;
+* ``stage_in`` / ``stage_out`` enqueue the copies on a caller-owned stream, so the copies of
+  one step overlap the kernel of another;
+* a ``region`` narrows a transfer to the block of rows (or heads) a rank computes when one
+  call is spread over several GPUs (``intent_b200.sharding``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+def _as_tensor(value) -> torch.Tensor:
+    if isinstance(value, torch.Tensor):
+        if value.device.type != "cpu" or value.layout != torch.strided:
+            raise ValueError("host staging takes ordinary CPU tensors (or NumPy arrays)")
+        return value
+    try:
+        import numpy
+    except ImportError:  # pragma: no cover
+        numpy = None
+    if numpy is not None and isinstance(value, numpy.ndarray):
+        return torch.from_numpy(value)
+    raise TypeError("host staging requires a NumPy array or a CPU tensor")
+
+
+def _whole(tensor: torch.Tensor) -> torch.Tensor:
+    """The complete storage behind a view, as bytes: views of one allocation share one device twin."""
+    storage = tensor.untyped_storage()
+    return torch.empty(0, dtype=torch.uint8).set_(storage, 0, (storage.nbytes(),), (1,))
+
+
+@dataclass
+class _Staged:
+    host: torch.Tensor              # the whole host allocation, as bytes
+    device: torch.Tensor            # its device twin, as bytes
+    writable: bool = False
+    saved: torch.Tensor | None = None
+    regions: list = field(default_factory=list)     # (host view, device view) pairs to copy in; empty = all
+
+
+class HostBuffers:
+    def __init__(self, device, *, page_lock: bool = True):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise ValueError("b200 calls run on CUDA devices")
+        self._page_lock = page_lock
+        self._staged: dict[tuple, _Staged] = {}
+        self._results: list[tuple] = []             # (device view, host view)
+        self._registered: list[int] = []
+        self.owned: list[torch.Tensor] = []
+
+    # ------------------------------------------------------------------ page locking
+    def _lock_pages(self, host_bytes: torch.Tensor) -> None:
+        if not self._page_lock or host_bytes.numel() == 0 or host_bytes.is_pinned():
+            return
+        runtime = torch.cuda.cudart()
+        status = runtime.cudaHostRegister(host_bytes.data_ptr(), host_bytes.numel(), 0)
+        if int(status) == 0:
+            self._registered.append(host_bytes.data_ptr())
+        # any other status (memory already registered, or not lockable): copies stay correct, only synchronous
+
+    # ------------------------------------------------------------------ inputs
+    def begin(self) -> None:
+        """Forget what earlier calls staged; device twins and page locks live until close()."""
+        self._staged.clear()
+        self._results.clear()
+
+    def input(self, value, *, writable: bool = False, preserve: bool = False, region=None) -> torch.Tensor:
+        """The device view to bind for a host operand.  Device tensors pass through.  `region`,
+        given as a function from a tensor to a view of it, narrows the transfers of this operand
+        to that view; the returned device tensor still has the operand's full shape."""
+        if isinstance(value, torch.Tensor) and value.device.type == "cuda":
+            if value.device != self.device:
+                raise ValueError(f"operand lives on {value.device}, the scope was opened for {self.device}")
+            return value
+        host = _as_tensor(value)
+        whole = _whole(host)
+        key = (whole.data_ptr(), whole.numel()) if whole.numel() else ("empty", id(value))
+        record = self._staged.get(key)
+        if record is None:
+            begin, end = whole.data_ptr(), whole.data_ptr() + whole.numel()
+            for other in self._staged.values():
+                other_begin = other.host.data_ptr()
+                if other.host.numel() and whole.numel() and begin < other_begin + other.host.numel() and other_begin < end:
+                    raise NotImplementedError("aliased host views must come from one complete allocation")
+            self._lock_pages(whole)
+            record = _Staged(whole, torch.empty(whole.numel(), dtype=torch.uint8, device=self.device))
+            self.owned.append(record.device)
+            self._staged[key] = record
+        record.writable |= writable
+        device_view = record.device.view(host.dtype).as_strided(tuple(host.shape), tuple(host.stride()),
+                                                                  host.storage_offset())
+        if region is not None:
+            record.regions.append((region(host), region(device_view)))
+        if preserve and record.saved is None:
+            record.saved = record.host.clone()
+        return device_view
+
+    def stage_in(self, stream=None) -> None:
+        """Enqueue the host-to-device copies of every staged operand (its regions, when narrowed)."""
+        with torch.cuda.stream(stream) if stream is not None else _null():
+            for record in self._staged.values():
+                if record.regions:
+                    for host_view, device_view in record.regions:
+                        device_view.copy_(host_view, non_blocking=True)
+                elif record.host.numel():
+                    record.device.copy_(record.host, non_blocking=True)
+
+    # ------------------------------------------------------------------ outputs and workspace
+    def workspace(self, shape, dtype) -> torch.Tensor:
+        tensor = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        self.owned.append(tensor)
+        return tensor
+
+    def retain_outputs(self, value) -> None:
+        """Keep runtime-allocated outputs alive until close()."""
+        if isinstance(value, dict):
+            value = tuple(value.values())
+        if isinstance(value, (tuple, list)):
+            for item in value:
+                self.retain_outputs(item)
+        elif isinstance(value, torch.Tensor) and all(value is not kept for kept in self.owned):
+            self.owned.append(value)
+
+    def result(self, value: torch.Tensor, *, region=None, into: torch.Tensor | None = None) -> torch.Tensor:
+        """Registers a device output for download and returns the page-locked host tensor it
+        lands in at stage_out() / finish().  `region` narrows the download like in `input`."""
+        self.retain_outputs(value)
+        host = into if into is not None else torch.empty_strided(tuple(value.shape), tuple(value.stride()),
+                                                                 dtype=value.dtype)
+        self._lock_pages(_whole(host))
+        pair = (value, host) if region is None else (region(value), region(host))
+        self._results.append(pair)
+        return host
+
+    def stage_out(self, stream=None) -> None:
+        """Enqueue the device-to-host copies: registered results, then writable staged operands."""
+        with torch.cuda.stream(stream) if stream is not None else _null():
+            for device_view, host_view in self._results:
+                host_view.copy_(device_view, non_blocking=True)
+            for record in self._staged.values():
+                if record.writable and record.host.numel():
+                    record.host.copy_(record.device, non_blocking=True)
+
+    def finish(self, stream=None) -> None:
+        """stage_out() and wait until the data is in host memory."""
+        self.stage_out(stream)
+        (stream if stream is not None else torch.cuda.current_stream(self.device)).synchronize()
+
+    def reset(self) -> None:
+        """Restore operands staged with preserve=True to the contents they had then."""
+        for record in self._staged.values():
+            if record.saved is not None:
+                record.host.copy_(record.saved)
+                record.device.copy_(record.host, non_blocking=True)
+
+    @property
+    def bytes_in(self) -> int:
+        total = 0
+        for record in self._staged.values():
+            if record.regions:
+                total += sum(view.numel() * view.element_size() for view, _ in record.regions)
+            else:
+                total += record.host.numel()
+        return total
+
+    @property
+    def bytes_out(self) -> int:
+        return (sum(view.numel() * view.element_size() for view, _ in self._results)
+                + sum(record.host.numel() for record in self._staged.values() if record.writable))
+
+    # ------------------------------------------------------------------ lifetime
+    def close(self) -> None:
+        if self._registered:
+            torch.cuda.synchronize(self.device)
+            runtime = torch.cuda.cudart()
+            for pointer in self._registered:
+                runtime.cudaHostUnregister(pointer)
+        self._registered.clear()
+        self._staged.clear()
+        self._results.clear()
+        self.owned.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        return False

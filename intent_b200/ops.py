@@ -103,12 +103,14 @@ def flash_attention(q, k, v, scale: float, out=None, *, head_group: int = 1, cau
     return out
 
 
-def csr_spmm(row_offsets, column_indices, values, dense, out=None):
+def csr_spmm(row_offsets, column_indices, values, dense, out=None, *, state=None):
+    """`state`: the call's int32 workspace (``workspace(device)`` by default); calls that may overlap
+    on different streams need one each."""
     device = _require_cuda(row_offsets, column_indices, values, dense)
     if out is None:
         out = torch.empty((row_offsets.numel() - 1, dense.shape[1]), dtype=torch.float32, device=device)
     _call("b200_csr_spmm", device, *_slots(row_offsets), *_slots(column_indices), *_slots(values),
-          *_slots(dense), *_slots(out), _stream(dense))
+          *_slots(dense), *_slots(out), *_slots(workspace(device) if state is None else state), _stream(dense))
     return out
 
 
@@ -184,13 +186,30 @@ def attention_backward_dq(q, k, v, grad_output, lse, delta, scale: float, *, hea
     return grad_q
 
 
-def csr_spmm_status(device) -> None:
+def csr_spmm_status(device, state=None) -> None:
     """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
     device = torch.device(device)
+    state = workspace(device) if state is None else state
     row = ctypes.c_int64(-1)
     with torch.cuda.device(device):
-        status = _native.entry("b200_csr_spmm_status")(ctypes.byref(row), torch.cuda.current_stream(device).cuda_stream)
+        status = _native.entry("b200_csr_spmm_status")(state.data_ptr(), ctypes.byref(row),
+                                                        torch.cuda.current_stream(device).cuda_stream)
     _native.check("b200_csr_spmm_status", status)
+
+
+def gather_probe(table: torch.Tensor, gathers: int, *, variant: int = 4, hints: bool = True) -> None:
+    """Enqueues the gather-rate probe over `table` (rows of 128 f32)."""
+    device = _require_cuda(table)
+    if table.dtype != torch.float32 or table.dim() != 2 or table.shape[1] != 128 or not table.is_contiguous():
+        raise ValueError("gather_probe takes a contiguous f32 table of 128 columns")
+    sink = _probe_sinks.get(device)
+    if sink is None:
+        sink = _probe_sinks[device] = torch.zeros(148 * 64 * 128 * 4, dtype=torch.float32, device=device)
+    _call("b200_gather_probe", device, table.data_ptr(), table.shape[0], int(gathers), int(variant), int(hints),
+          sink.data_ptr(), workspace(device).data_ptr(), _stream(table))
+
+
+_probe_sinks: dict[torch.device, torch.Tensor] = {}
 
 
 def csr_validate(row_offsets, column_indices, columns: int) -> None:

@@ -19,14 +19,14 @@ the reference's own GPU providers (``python/intent/targets/triton.py:10-51``):
 from __future__ import annotations
 
 from dataclasses import dataclass
-from functools import partial
 from typing import ClassVar
 
 from intent.runtime import CompiledArtifact
 from intent.runtime.native import NativePreparedRuntime
-from intent.targets.execution import indexed_key, indexed_target, torch_storage
+from intent.targets.execution import indexed_key, torch_storage
 from intent.targets.nvidia import NVIDIATarget
 from intent.targets.nvidia.specification import read_nvidia_target
+from intent.targets.nvidia.target import ResolvedNVIDIATarget
 from intent.targets.provider import EnvironmentCheck, LocalExecution, Provider
 
 from . import _native
@@ -78,9 +78,32 @@ def _read_facts(source, metadata, abi):
     return B200Facts.read(metadata)
 
 
+@dataclass(frozen=True, slots=True)
+class ResolvedB200Target(ResolvedNVIDIATarget):
+    """A resolved device plus the two local options of this provider.  ``gpus`` (number of
+    ranks, or their CUDA ordinals in rank order) and ``gather_output`` spread one call over
+    the processes of a ``torch.distributed`` group, one per GPU (``intent_b200.sharding``);
+    the reference's own providers are single-device
+    (``python/intent/targets/local.py:36-45``)."""
+    gpus: object = None
+    gather_output: bool = False
+
+
+def _resolve(device, *, workers, gpus=None, gather_output=False):
+    """``LocalExecution.resolve`` (called from ``python/intent/targets/local.py:60-67`` with the
+    whitelisted ``backend_options`` as keywords)."""
+    if workers is not None:
+        raise ValueError("workers is a CPU execution budget")
+    plain = B200Target(device=device.index).resolve()
+    frozen = tuple(gpus) if isinstance(gpus, (list, tuple)) else gpus
+    return ResolvedB200Target(plain.compilation, plain.device, frozen, bool(gather_output))
+
+
 def _bind(program, target):
     _native.check("b200_device_check", _native.entry("b200_device_check")(int(target.device)))
-    runtime = B200Runtime(B200Program(program.metadata, target.device), program.interface)
+    program_runtime = B200Program(program.metadata, target.device, gpus=getattr(target, "gpus", None),
+                                  gather_output=getattr(target, "gather_output", False))
+    runtime = B200Runtime(program_runtime, program.interface)
     return CompiledArtifact(program.source, program.ir, target.device, runtime, None, device_type="cuda")
 
 
@@ -101,5 +124,5 @@ def _environment_checks(target):
 
 PROVIDER = Provider(
     "gpu", B200Target, _read_facts, _bind, _environment_checks,
-    LocalExecution("cuda", True, frozenset(), partial(indexed_target, B200Target), indexed_key, torch_storage),
+    LocalExecution("cuda", True, frozenset({"gpus", "gather_output"}), _resolve, indexed_key, torch_storage),
     "b200_native", read_nvidia_target)

@@ -31,7 +31,7 @@ from threading import RLock
 
 import torch
 
-from . import _native
+from . import _native, sharding
 
 IN, OUT, INOUT = 0, 1, 2
 
@@ -106,69 +106,90 @@ def _overlap(lhs, rhs) -> bool:
     return lhs[0] < lhs[1] and rhs[0] < rhs[1] and lhs[0] < rhs[1] and rhs[0] < lhs[1]
 
 
+def _stride_rule(rule):
+    """One entry of a view's "strides" list: free (None), a fixed element stride, or a named
+    symbol that several axes must agree on."""
+    if rule is None or type(rule) is int:
+        return rule
+    if isinstance(rule, dict) and rule.get("kind") == "stride_symbol":
+        return StrideSymbol(rule["symbol"])
+    raise ValueError(f"interface: cannot interpret the stride rule {rule!r}")
+
+
+def _view_parameter(position: int, record: dict) -> ViewParameter:
+    name = record["name"]
+    extents = tuple(record["shape"])
+    identities = tuple(record["dimensions"])
+    rules = tuple(_stride_rule(rule) for rule in record["strides"])
+    for extent in extents:
+        if type(extent) is not int or extent < -1:
+            raise ValueError(f"interface: {name} has the extent {extent!r}; extents are integers, -1 when dynamic")
+    if not len(extents) == len(identities) == len(rules):
+        raise ValueError(f"interface: {name} lists {len(extents)} extents, {len(identities)} dimension ids "
+                         f"and {len(rules)} stride rules; the three must have the view's rank")
+    if record["access"] not in (IN, OUT, INOUT):
+        raise ValueError(f"interface: {name} has the access code {record['access']!r} (0 In, 1 Out, 2 InOut)")
+    if record["alias"] and record["noalias"]:
+        raise ValueError(f"interface: {name} names an alias group and is noalias at once")
+    return ViewParameter(position, name, record["dtype"], extents, identities, rules, record["access"],
+                         record["alias"], record["noalias"])
+
+
 @dataclass(frozen=True)
 class Interface:
-    """The author's ordered runtime parameters, independent of the device ABI."""
+    """The author's ordered runtime parameters, independent of the device ABI
+    (the "interface" object of artifact.json)."""
     parameters: tuple
 
     @classmethod
     def read(cls, metadata: dict) -> "Interface":
-        parameters, names = [], set()
-        for position, entry in enumerate(metadata["parameters"]):
-            name = entry["name"]
-            if not isinstance(name, str) or not name or name in names:
-                raise ValueError("public parameter names must be nonempty and unique")
-            names.add(name)
-            if entry["dtype"] not in _DTYPE_BYTES:
-                raise NotImplementedError(f"element type {entry['dtype']!r} is not supported by b200")
-            if entry["kind"] == "scalar":
-                parameters.append(ScalarParameter(position, name, entry["dtype"]))
-                continue
-            if entry["kind"] != "view":
-                raise ValueError("public interface parameter must be a view or scalar")
-            shape, dimensions = tuple(entry["shape"]), tuple(entry["dimensions"])
-            if any(type(extent) is not int or extent < -1 for extent in shape):
-                raise ValueError("public shape requires static extents or dynamic -1")
-            if len(dimensions) != len(shape):
-                raise ValueError("public dimension identities must match view rank")
-            strides = []
-            for constraint in entry["strides"]:
-                if constraint is None or type(constraint) is int:
-                    strides.append(constraint)
-                elif isinstance(constraint, dict) and constraint.get("kind") == "stride_symbol":
-                    strides.append(StrideSymbol(constraint["symbol"]))
-                else:
-                    raise ValueError("unsupported public stride constraint")
-            if len(strides) != len(shape):
-                raise ValueError("public stride constraints must match view rank")
-            if entry["alias"] and entry["noalias"]:
-                raise ValueError("alias and noalias are mutually exclusive")
-            if entry["access"] not in (IN, OUT, INOUT):
-                raise ValueError("public access must be 0 (In), 1 (Out) or 2 (InOut)")
-            parameters.append(ViewParameter(position, name, entry["dtype"], shape, dimensions,
-                                            tuple(strides), entry["access"], entry["alias"], entry["noalias"]))
-        return cls(tuple(parameters))
+        records = metadata["parameters"]
+        names = [record["name"] for record in records]
+        if any(not isinstance(name, str) or not name for name in names) or len(set(names)) != len(names):
+            raise ValueError(f"interface: parameter names {names!r} are not distinct non-empty strings")
+        parsed = []
+        for position, record in enumerate(records):
+            if record["dtype"] not in _DTYPE_BYTES:
+                raise NotImplementedError(f"element type {record['dtype']!r} is not supported by b200")
+            kind = record["kind"]
+            if kind == "view":
+                parsed.append(_view_parameter(position, record))
+            elif kind == "scalar":
+                parsed.append(ScalarParameter(position, record["name"], record["dtype"]))
+            else:
+                raise ValueError(f"interface: {record['name']} is a {kind!r}; only views and scalars cross the ABI")
+        return cls(tuple(parsed))
+
+    def _select(self, keep) -> tuple:
+        return tuple(parameter for parameter in self.parameters if keep(parameter))
 
     @property
     def views(self):
-        return tuple(p for p in self.parameters if isinstance(p, ViewParameter))
-
-    @property
-    def inputs(self):
-        return tuple(p for p in self.parameters if not isinstance(p, ViewParameter) or not p.output)
+        return self._select(lambda parameter: isinstance(parameter, ViewParameter))
 
     @property
     def outputs(self):
-        return tuple(p for p in self.views if p.output)
+        return self._select(lambda parameter: isinstance(parameter, ViewParameter) and parameter.output)
+
+    @property
+    def inputs(self):
+        """What a caller supplies when the runtime allocates the outputs: scalars and every
+        view that is not a pure output."""
+        declared_outputs = self.outputs
+        return self._select(lambda parameter: parameter not in declared_outputs)
 
     def explicit_arguments(self, arguments: tuple, outputs: tuple) -> tuple:
-        if len(arguments) != len(self.inputs):
-            raise TypeError(f"expected {len(self.inputs)} input arguments, got {len(arguments)}")
-        if len(outputs) != len(self.outputs):
-            raise TypeError(f"expected {len(self.outputs)} explicit output buffers, got {len(outputs)}")
-        supplied, allocated = iter(arguments), iter(outputs)
-        return tuple(next(allocated) if isinstance(p, ViewParameter) and p.output else next(supplied)
-                     for p in self.parameters)
+        """Merges inputs and caller-owned output buffers back into declaration order."""
+        wanted_inputs, wanted_outputs = len(self.inputs), len(self.outputs)
+        if len(arguments) != wanted_inputs:
+            raise TypeError(f"expected {wanted_inputs} input arguments, got {len(arguments)}")
+        if len(outputs) != wanted_outputs:
+            raise TypeError(f"expected {wanted_outputs} explicit output buffers, got {len(outputs)}")
+        pending = {True: list(reversed(outputs)), False: list(reversed(arguments))}
+        merged = []
+        for parameter in self.parameters:
+            merged.append(pending[isinstance(parameter, ViewParameter) and parameter.output].pop())
+        return tuple(merged)
 
 
 # --------------------------------------------------------------------------- native layout
@@ -316,7 +337,7 @@ class B200Program:
 
     device_type = "cuda"
 
-    def __init__(self, metadata: dict, device: int | torch.device):
+    def __init__(self, metadata: dict, device: int | torch.device, *, gpus=None, gather_output: bool = False):
         if metadata.get("provider") != "b200":
             raise ValueError("not a b200 program")
         self.metadata = metadata
@@ -324,6 +345,9 @@ class B200Program:
         self.interface = self.layout.interface
         self.facts = B200Facts.read(metadata)
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        # the gpus / gather_output backend options: this rank's place among the processes that
+        # share the call, or None for a call that stays on one GPU
+        self.distribution = sharding.distribution(gpus, gather_output, self.device)
         self._observation: Observation | None = None
         self._lock = RLock()
         self._function = None
@@ -497,8 +521,25 @@ class B200Program:
         description = tuple(
             (p.name, facts[p.position].shape, facts[p.position].strides) if isinstance(p, ViewParameter)
             else (p.name, ordered[p.position]) for p in self.interface.parameters)
-        return B200Call(self, ordered, self._native_arguments(ordered, facts, workspace_facts), outputs,
-                        tuple(owners), description)
+        blocks = ()
+        if self.distribution is not None:
+            # The full operands were validated above.  The native call now receives this rank's
+            # block of them (views into the same buffers), and the output blocks are remembered
+            # for the optional all-gather after the launch.
+            constants = {name: value for name, _, value in self.facts.tail}
+            part = sharding.partition(self.facts.family, ordered, self.distribution.rank, self.distribution.world,
+                                      head_group=int(constants.get("head_group", 1)))
+            blocks = part.outputs
+            launched = part.arguments
+            facts = {p.position: ViewFacts(tuple(launched[p.position].shape), tuple(launched[p.position].stride()),
+                                           launched[p.position].data_ptr(), None, None, None)
+                     for p in self.interface.views}
+            description += (("shard", (part.begin, part.end), part.units),)
+            owners.extend(t for t in launched if isinstance(t, torch.Tensor))
+        else:
+            launched = ordered
+        return B200Call(self, ordered, self._native_arguments(launched, facts, workspace_facts), outputs,
+                        tuple(owners[:len(self.layout.workspaces)]), description, tuple(owners), blocks)
 
     def prepare_call(self, arguments: tuple, *, outputs: tuple | None = None) -> "B200Call":
         if outputs is None:
@@ -537,6 +578,8 @@ class B200Call:
     outputs: tuple
     workspaces: tuple
     description: tuple
+    owners: tuple = ()            # tensors the native arguments point into (workspaces, shard views)
+    blocks: tuple = ()            # output blocks of a call that is spread over several GPUs
     _observation: Observation | None = field(default=None, repr=False)
 
     def compile(self) -> None:
@@ -558,7 +601,19 @@ class B200Call:
         if status != _native.OK:
             self._record("failed")
             _native.check(self.program.facts.entry, status)
+        self.gather()
         self._record("launched")
+
+    def gather(self) -> None:
+        """The final all-gather of a call spread over several GPUs (`gather_output`): every
+        rank's output block reaches every rank, in place, ordered after the kernel on torch's
+        current stream.  A call on one GPU, or without `gather_output`, does nothing here."""
+        distribution = self.program.distribution
+        if distribution is None or not distribution.gather_output:
+            return
+        with torch.cuda.device(self.program.device):
+            for block in self.blocks:
+                sharding.gather_blocks(block, distribution.world, group=distribution.group)
 
     def enqueue(self, queue) -> None:
         """Submit on a caller-owned CUDA stream (a ``torch.cuda.Stream`` or a raw handle)
@@ -569,6 +624,11 @@ class B200Call:
         if status != _native.OK:
             self._record("failed")
             _native.check(self.program.facts.entry, status)
+        if self.blocks and self.program.distribution.gather_output:
+            if not hasattr(queue, "cuda_stream"):
+                raise NotImplementedError("gather_output on a caller-owned stream needs a torch.cuda.Stream")
+            with torch.cuda.stream(queue):
+                self.gather()
         self._record("launched")
 
     def result(self):

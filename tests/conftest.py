@@ -1,4 +1,3 @@
-import os
 import sys
 from pathlib import Path
 
@@ -9,8 +8,13 @@ ROOT = Path(__file__).resolve().parents[1]
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-# the reference checkout: named by INTENT_REFERENCE, else looked for beside this repository
-REFERENCE_PYTHON = Path(os.environ.get("INTENT_REFERENCE", ROOT.parent / "reference")) / "python"
+# The unmodified reference package the provider is tested through: installed (copied) from the
+# checkout into baseline/_ref where a checkout exists, and found there on machines without one.
+from intent_b200 import build as _build
+
+_installed = _build.install_reference()
+REFERENCE_PYTHON = _installed if _installed is not None else ROOT / "baseline" / "_ref"
+HAS_REFERENCE = (REFERENCE_PYTHON / "intent" / "__init__.py").is_file()
 
 
 def pytest_configure(config):

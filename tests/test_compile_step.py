@@ -54,7 +54,8 @@ def test_classification_and_metadata(name):
     layout = NativeLayout.read(metadata)                         # the NativeABI flavour parses
     assert metadata["target"] == {"family": "b200_native", "capabilities": b200.B200_CAPABILITIES}
     assert metadata["compile_options"] == {"numerics": "source", "optimizations": {}, "optimization_remarks": False}
-    assert bool(layout.workspaces) == (family in {"gemm", "flash_attention", "attention_backward_dkdv", "attention_backward_dq"})
+    assert bool(layout.workspaces) == (family in {"gemm", "flash_attention", "attention_backward_dkdv", "attention_backward_dq",
+                                                 "csr_spmm"})
 
 
 def test_interface_of_softmax_keeps_author_constraints():
