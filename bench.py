@@ -793,6 +793,49 @@ def measure_resident(case, steps: int, warmup: int, distributed: bool, world: in
     return result
 
 
+def gather_ceiling(case, result: dict) -> dict:
+    """What bounds the SpMM gathers on this device, measured beside the SpMM figure: the rate of
+    random 512-byte row reads (`b200_gather_probe`) out of a table that fits L2 (a quarter of X)
+    and out of all of X in one pass.  The SpMM call moves nnz * 512 bytes of such reads, so its time
+    cannot go below that volume over the L2-resident rate; a single pass over all of X cannot go
+    below the volume over the all-of-X rate."""
+    from intent_b200 import ops
+    dense = case.host[3].to(case.device)
+    gathers = case.host[1].numel()
+    volume = gathers * 512.0
+    names = {0: "4 loads in flight per lane", 1: "8 loads in flight per lane", 2: "16 loads in flight per lane"}
+    rates = {}
+    for label, table in (("l2_resident", dense[:65536]), ("all_of_x", dense)):
+        best = None
+        for variant in (0, 1, 2):
+            for hints in (False, True):
+                launch = lambda step, v=variant, h=hints, tb=table: ops.gather_probe(tb, gathers, variant=v, hints=h)
+                for _ in range(2):
+                    launch(0)
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                for _ in range(3):
+                    launch(0)
+                stop.record()
+                torch.cuda.synchronize()
+                rate = volume * 3 / start.elapsed_time(stop) / 1e9          # TB/s
+                if best is None or rate > best[0]:
+                    best = (rate, f"{names[variant]}, {'evict_last' if hints else 'no'} hint")
+        rates[label] = {"tb_per_s": best[0], "form": best[1]}
+    ops.workspace_status(case.device)
+    floor_ms = volume / rates["l2_resident"]["tb_per_s"] / 1e9
+    one_pass_ms = volume / rates["all_of_x"]["tb_per_s"] / 1e9
+    return {"gather_bytes_per_call": volume, "probe": rates,
+            "spmm_gather_tb_per_s": volume / result["ms_per_step"] / 1e9,
+            "floor_ms_at_l2_gather_rate": floor_ms, "spmm_over_floor": result["ms_per_step"] / floor_ms,
+            "one_pass_ms_at_all_of_x_rate": one_pass_ms, "spmm_over_one_pass": result["ms_per_step"] / one_pass_ms,
+            "note": "floor = the call's nnz x 512 B of row gathers at the probe's L2-resident rate (what column "
+                    "blocks that stay in L2 could reach with free Y traffic); one_pass = the same volume at the "
+                    "rate a single pass over all of X reaches (X is 134 MB; a gathered line is cached by the L2 "
+                    "half next to the SM that asked, so about 60 MB of distinct X stay resident)"}
+
+
 OUTPUT_BYTES = {"softmax": 4096 * 1024 * 4, "layer_norm": 16384 * 4096 * 2, "gemm": 8192 * 8192 * 2,
                 "attention": 8 * 32 * 4096 * 128 * 2, "spmm": 262144 * 128 * 4, "softmax_backward": 4096 * 4097 * 4,
                 "spmv": 32768 * 4}

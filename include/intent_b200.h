@@ -283,12 +283,12 @@ int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2
  *
  * The workspace is invocation-owned like the reference's native workspaces
  * (python/intent/runtime/native.py:207-209): B200_WORKSPACE_WORDS int32 words,
- * zeroed once by the caller.  Words 0-1 are the timeout report read by
- * b200_csr_spmm_status; word 2 carries, from the first launch of a call to its
- * later ones, whether every row ascends (a call on an X larger than L2 runs as
- * several launches over column blocks, and falls back to one pass in storage
- * order when a row does not ascend).  All state of a call lives in its
- * workspace: calls with distinct workspaces may overlap on different streams.
+ * zeroed once by the caller.  Word 2 carries, from the first launch of a call
+ * to its later ones, whether every row ascends (a call on an X larger than L2
+ * runs as several launches over column blocks, and falls back to one pass in
+ * storage order when a row does not ascend); words 0-1 are not written (the
+ * kernels have no bounded wait).  All state of a call lives in its workspace:
+ * calls with distinct workspaces may overlap on different streams.
  */
 int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_s0,
                   const void *column_indices, int64_t ci_d0, int64_t ci_s0,
@@ -321,21 +321,11 @@ int b200_csr_validate(const void *row_offsets, int64_t rows, const void *column_
                       int64_t nnz, int64_t columns, int64_t *where, void *stream);
 
 /*
- * b200_csr_spmm waits for its staged gathers with a bound.  If such a wait
- * ever gave up, the affected row was left unwritten and words 0-1 of the
- * call's workspace were set; this call synchronises `stream`, returns
- * B200_ERR_DEVICE_TIMEOUT (clearing the words) and stores the row in *row
- * (may be null), else B200_OK.  No counterpart in the reference.
- */
-int b200_csr_spmm_status(const void *workspace, int64_t *row, void *stream);
-
-/*
  * Measures what bounds the SpMM gathers on this device: `gathers` reads of
  * 512-byte rows at pseudo-random positions of `table` (table_rows x 128 f32).
- * variant 0..3: 4, 8, 16, 32 loads in flight per lane (64 warps per SM);
- * variant 4: staged through shared memory by the copy engine as b200_csr_spmm
- * does.  hints != 0 asks L2 to keep the gathered lines.  `sink` (>= 1 MiB) is
- * never written in practice; `workspace` as for b200_csr_spmm.  A measurement
+ * variant 0..3: 4, 8, 16, 32 loads in flight per lane (64 warps per SM).
+ * hints != 0 asks L2 to keep the gathered lines.  `sink` (>= 5 MiB) is never
+ * written in practice; `workspace` as for b200_csr_spmm.  A measurement
  * aid with no counterpart in the reference: bench.py times it to report the
  * gather ceiling beside the SpMM figure.
  */

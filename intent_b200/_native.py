@@ -46,7 +46,6 @@ SIGNATURES = {
     "b200_attention_backward_dkdv": _view(4) * 4 + _view(3) * 2 + _view(4) * 2 + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_attention_backward_dq": _view(4) * 4 + _view(3) * 2 + _view(4) + [_F32] + _view(1) + [_I32, _I32, _I32, _P],
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
-    "b200_csr_spmm_status": [_P, ctypes.POINTER(_I64), _P],
     "b200_gather_probe": [_P, _I64, _I64, _I32, _I32, _P, _P, _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],
     "b200_device_check": [ctypes.c_int],

@@ -15,6 +15,9 @@
 // Work per launch: 2*M*N*K flop; compulsory traffic (M*K + K*N + M*N)*2 bytes.
 // Tiles are walked in groups of kGroupM row-tiles per B column-tile so the
 // CTAs running together share A/B panels through L2.
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -252,6 +255,257 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
+// ---------------------------------------------------------------------------
+// CTA-pair kernel (cta_group::2).  Two CTAs on the two SMs of a TPC share one 256 x 256 tile:
+// each loads its own 128 rows of A and its own 128 of B's 256 columns (plain unicast TMA, no
+// multicast), the pair's leader issues tcgen05.mma over M = 256, and each CTA ends up with its
+// 128 rows of the accumulator in its own TMEM.  Against the single-CTA 128 x 256 tile this
+// halves the bytes of B an SM pulls from L2 and reads from shared memory per flop (32 KB per
+// 64-deep K block and CTA instead of 48 KB).  The epilogue goes TMEM -> registers -> 128-byte
+// swizzled shared memory -> cp.async.bulk.tensor store, so C leaves the SM as full 128-byte
+// rows of a 128 x 64 box instead of 32 scattered 64-byte pieces per warp store.
+//   warp 0      TMA producer (every CTA; completion bytes counted on the leader's barrier)
+//   warp 1      MMA issuer (leader only); both CTAs' warp 1 allocate / free TMEM together
+//   warps 2..5  epilogue, two staging buffers, one thread issues the stores
+// Requires B K-major and a C that TMA can store (16-byte aligned base, pitch a multiple of 8).
+// ---------------------------------------------------------------------------
+namespace pair {
+
+constexpr int kTileM = 256, kTileN = 256;      // per pair
+constexpr int kCtaM = 128, kCtaN = 128;        // rows of A / columns of B each CTA loads
+constexpr int kStages = 6;
+constexpr uint32_t kBytesA = kCtaM * kBlockK * 2;
+constexpr uint32_t kBytesB = kCtaN * kBlockK * 2;
+constexpr uint32_t kStageBytes = kBytesA + kBytesB;             // 32 KB
+constexpr int kStoreColumns = 64;                                // one 128-byte swizzle span of 16-bit elements
+constexpr uint32_t kStoreBytes = kCtaM * kStoreColumns * 2;     // 16 KB
+constexpr int kStoreBuffers = 2;
+constexpr int kEpilogueBarrier = 1;                              // named barrier of the four epilogue warps
+
+struct __align__(8) Barriers {
+  uint64_t full[kStages];        // leader's: both CTAs' tiles of a stage have landed
+  uint64_t empty[kStages];       // every CTA's own: the pair's MMAs have read the stage
+  uint64_t tmem_full[kAccumulators];
+  uint64_t tmem_empty[kAccumulators];   // leader's: both CTAs' epilogues have drained the accumulator
+  uint32_t tmem_base;
+  int abort_flag;
+  int epilogue_abort;            // an epilogue warp gave up: the four warps leave together
+};
+
+constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + kStoreBuffers * kStoreBytes + sizeof(Barriers);
+
+struct TileWalk {
+  int tiles_m, tiles_n, total;
+  __device__ void locate(int tile, int *m, int *n) const {
+    const int group_rows = kGroupM / 2;                 // 8 pair tiles = the 16 row tiles of the single-CTA walk
+    const int group_span = group_rows * tiles_n;
+    const int group = tile / group_span;
+    const int first_m = group * group_rows;
+    const int rows_in_group = min(group_rows, tiles_m - first_m);
+    const int within = tile - group * group_span;
+    *m = first_m + within % rows_in_group;
+    *n = within / rows_in_group;
+  }
+};
+
+// A wait that gives up also raises the peer's abort flag, so the pair winds down together.
+__device__ __forceinline__ bool wait(uint64_t *bar, uint32_t parity, Barriers *bars, uint32_t peer, int *status, int site) {
+  if (tc::mbar_wait(bar, parity, &bars->abort_flag, status, site)) return true;
+  tc::store_cluster_u32(tc::cluster_address(tc::smem_u32(&bars->abort_flag), peer), 1u);
+  return false;
+}
+
+template <typename T, bool RELU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, int m, int n, int k, int *status) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char *tiles = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+  unsigned char *staging = tiles + kStages * kStageBytes;
+  Barriers *bars = reinterpret_cast<Barriers *>(staging + kStoreBuffers * kStoreBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int pairs = gridDim.x / 2, pair_id = blockIdx.x / 2;
+  TileWalk walk;
+  walk.tiles_m = (m + kTileM - 1) / kTileM;
+  walk.tiles_n = (n + kTileN - 1) / kTileN;
+  walk.total = walk.tiles_m * walk.tiles_n;
+  const int k_blocks = (k + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&bars->full[s], 1);
+      tc::mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < kAccumulators; ++a) {
+      tc::mbar_init(&bars->tmem_full[a], 1);
+      tc::mbar_init(&bars->tmem_empty[a], 2 * kEpilogueThreads / 32);   // four warps of each CTA
+    }
+    bars->abort_flag = 0;
+    bars->epilogue_abort = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_descriptor(&map_a);
+    tc::tma_prefetch_descriptor(&map_b);
+    tc::tma_prefetch_descriptor(&map_c);
+  }
+  if (warp == 1) tc::tmem_alloc_pair(&bars->tmem_base, kTmemColumns);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();            // the peer's barriers exist before anything arrives on them
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (tc::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued = 0;
+      bool alive = true;
+      for (int tile = pair_id; alive && tile < walk.total; tile += pairs) {
+        int tm, tn;
+        walk.locate(tile, &tm, &tn);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!wait(&bars->empty[stage], phase ^ 1, bars, rank ^ 1, status, tc::kSiteProducerEmpty)) {
+            alive = false;
+            break;
+          }
+          unsigned char *slot = tiles + stage * kStageBytes;
+          const uint32_t leader_full = tc::cluster_address(tc::smem_u32(&bars->full[stage]), 0);
+          if (leader) tc::mbar_expect_tx(&bars->full[stage], 2 * kStageBytes);   // both CTAs' bytes
+          tc::tma_load_2d_pair(slot, &map_a, leader_full, kb * kBlockK, tm * kTileM + (int)rank * kCtaM);
+          tc::tma_load_2d_pair(slot + kBytesA, &map_b, leader_full, kb * kBlockK, tn * kTileN + (int)rank * kCtaN);
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!alive && leader) {
+        // Let copies already in flight (the peer's too: they complete on these barriers) land
+        // before the pair's shared memory is released.
+        const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
+        for (uint32_t back = 1; back <= pending; ++back) {
+          const uint32_t slot_index = issued - back;
+          const uint32_t s = slot_index % kStages, ph = (slot_index / kStages) & 1;
+          const long long start = clock64();
+          while (!tc::mbar_try_wait(&bars->full[s], ph) && clock64() - start < tc::kWaitCycles / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer
+    if (leader && tc::elect_one()) {
+      constexpr uint32_t idesc = tc::instr_desc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, kTileM, kTileN, false);
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool alive = true;
+      for (int tile = pair_id; alive && tile < walk.total; tile += pairs) {
+        if (!wait(&bars->tmem_empty[acc], acc_phase ^ 1, bars, 1, status, tc::kSiteMmaTmemEmpty)) break;
+        tc::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!wait(&bars->full[stage], phase, bars, 1, status, tc::kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          tc::tc_fence_after_sync();
+          const uint32_t a_address = tc::smem_u32(tiles + stage * kStageBytes);
+          const uint64_t desc_a = tc::smem_desc_k_major_sw128(a_address);
+          const uint64_t desc_b = tc::smem_desc_k_major_sw128(a_address + kBytesA);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
+            tc::mma_f16_ss_pair(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
+          tc::mma_commit_pair(&bars->empty[stage], 3);   // frees the slot in both CTAs
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!alive) break;
+        tc::mma_commit_pair(&bars->tmem_full[acc], 3);
+        if (++acc == kAccumulators) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int quadrant = warp & 3;                      // TMEM lanes [32 * quadrant, +32) belong to this warp
+    const int row_in_tile = quadrant * 32 + lane;       // of this CTA's 128 rows
+    const bool issuer = warp == 2 && lane == 0;
+    const uint32_t leader_empty0 = tc::cluster_address(tc::smem_u32(&bars->tmem_empty[0]), 0);
+    const uint32_t leader_empty1 = tc::cluster_address(tc::smem_u32(&bars->tmem_empty[1]), 0);
+    uint32_t acc = 0, acc_phase = 0;
+    uint32_t buffer = 0;
+    for (int tile = pair_id; tile < walk.total; tile += pairs) {
+      int tm, tn;
+      walk.locate(tile, &tm, &tn);
+      // The four warps meet at named barriers below, so they must take the same way out: a warp
+      // whose wait gave up says so in shared memory, and all of them decide after one barrier.
+      if (!wait(&bars->tmem_full[acc], acc_phase, bars, rank ^ 1, status, tc::kSiteEpilogueTmemFull))
+        bars->epilogue_abort = 1;
+      asm volatile("bar.sync %0, %1;" ::"n"(kEpilogueBarrier), "n"(kEpilogueThreads) : "memory");
+      if (*reinterpret_cast<volatile int *>(&bars->epilogue_abort)) break;
+      tc::tc_fence_after_sync();
+      const int row0 = tm * kTileM + (int)rank * kCtaM;
+      const int column0 = tn * kTileN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < kTileN / kStoreColumns; ++chunk) {
+        // the store that read this staging buffer two chunks ago has finished reading it
+        if (issuer) tc::tma_store_wait_read<kStoreBuffers - 1>();
+        asm volatile("bar.sync %0, %1;" ::"n"(kEpilogueBarrier), "n"(kEpilogueThreads) : "memory");
+        unsigned char *out = staging + buffer * kStoreBytes + row_in_tile * 128;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tc::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + acc * kTileN +
+                                  chunk * kStoreColumns + half * 32, v);
+          tc::tmem_load_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              f[i] = __uint_as_float(v[q * 8 + i]);
+              if (RELU) f[i] = (f[i] != f[i]) ? f[i] : fmaxf(f[i], 0.0f);
+            }
+            uint4 packed;
+            packed.x = pack2<T>(f[0], f[1]);
+            packed.y = pack2<T>(f[2], f[3]);
+            packed.z = pack2<T>(f[4], f[5]);
+            packed.w = pack2<T>(f[6], f[7]);
+            // 128-byte swizzle: the 16-byte piece c of row r sits at piece c ^ (r & 7)
+            const int piece = (half * 4 + q) ^ (row_in_tile & 7);
+            *reinterpret_cast<uint4 *>(out + piece * 16) = packed;
+          }
+        }
+        if (chunk == kTileN / kStoreColumns - 1) {
+          // the accumulator is in registers / shared memory: hand it back to the MMA issuer
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+        }
+        tc::fence_async_shared();
+        asm volatile("bar.sync %0, %1;" ::"n"(kEpilogueBarrier), "n"(kEpilogueThreads) : "memory");
+        if (issuer) {
+          tc::tma_store_2d(&map_c, staging + buffer * kStoreBytes, column0 + chunk * kStoreColumns, row0);
+          tc::tma_store_commit();
+        }
+        buffer ^= 1;
+      }
+      if (++acc == kAccumulators) { acc = 0; acc_phase ^= 1; }
+    }
+    if (issuer) tc::tma_store_wait<0>();                // C is written before the CTA leaves
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();            // neither CTA frees TMEM or shared memory the other may still use
+  if (warp == 1) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc_pair(tmem_base, kTmemColumns);
+  }
+}
+
+}  // namespace pair
+
 // C = 0 for an empty reduction (K == 0).
 template <typename T>
 __global__ void zero_fill_kernel(T *c, int64_t c_pitch, int m, int n) {
@@ -298,6 +552,61 @@ int cached_map_2d(CUtensorMap *out, const void *base, uint64_t inner, uint64_t o
   return B200_OK;
 }
 
+// CTA pairs the device runs at once (one CTA per SM; cached per device).
+int resident_pairs(const void *kernel) {
+  static std::mutex lock;
+  static int known[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return sm_count() / 2;
+  std::lock_guard<std::mutex> guard(lock);
+  if (known[device] == 0) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)(sm_count() / 2 * 2));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = pair::kSmemBytes;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters < 1) clusters = sm_count() / 2;
+    known[device] = clusters < sm_count() / 2 ? clusters : sm_count() / 2;
+  }
+  return known[device];
+}
+
+template <typename T>
+int gemm_pair_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, int64_t a_pitch, int64_t b_pitch,
+                    int64_t c_pitch, int relu, int *status, cudaStream_t stream) {
+  CUtensorMap map_a, map_b, map_c;
+  int result = cached_map_2d(&map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)a_pitch * 2, kBlockK, pair::kCtaM);
+  if (result != B200_OK) return result;
+  result = cached_map_2d(&map_b, b, (uint64_t)k, (uint64_t)n, (uint64_t)b_pitch * 2, kBlockK, pair::kCtaN);
+  if (result != B200_OK) return result;
+  result = cached_map_2d(&map_c, c, (uint64_t)n, (uint64_t)m, (uint64_t)c_pitch * 2, pair::kStoreColumns, pair::kCtaM);
+  if (result != B200_OK) return result;
+  auto kernel = relu ? pair::gemm_pair_kernel<T, true> : pair::gemm_pair_kernel<T, false>;
+  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, pair::kSmemBytes));
+  const int64_t tiles = ((m + pair::kTileM - 1) / pair::kTileM) * ((n + pair::kTileN - 1) / pair::kTileN);
+  const int64_t resident = resident_pairs(reinterpret_cast<const void *>(kernel));
+  const int pairs = (int)(tiles < resident ? tiles : resident);
+  kernel<<<2 * pairs, kThreads, pair::kSmemBytes, stream>>>(map_a, map_b, map_c, (int)m, (int)n, (int)k, status);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+// INTENT_B200_GEMM_KERNEL = single | pair overrides the choice below (read at every call).
+bool use_pair_kernel(bool eligible, int64_t m, int64_t n) {
+  const char *choice = getenv("INTENT_B200_GEMM_KERNEL");
+  if (choice && strcmp(choice, "single") == 0) return false;
+  if (choice && strcmp(choice, "pair") == 0) return eligible;
+  // a pair works on 256 x 256 tiles: worth it once the problem has a wave of them
+  return eligible && ((m + 255) / 256) * ((n + 255) / 256) >= sm_count() / 2;
+}
+
 template <typename T>
 int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, int64_t a_pitch,
                int64_t b_pitch, int64_t c_pitch, int relu, bool b_n_major, int *status, cudaStream_t stream) {
@@ -306,6 +615,9 @@ int gemm_typed(const T *a, const T *b, T *c, int64_t m, int64_t n, int64_t k, in
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
   }
+  const bool storable = aligned16(c) && c_pitch % 8 == 0 && c_pitch >= n;
+  if (use_pair_kernel(!b_n_major && storable, m, n))
+    return gemm_pair_typed<T>(a, b, c, m, n, k, a_pitch, b_pitch, c_pitch, relu, status, stream);
   CUtensorMap map_a, map_b;
   int result = cached_map_2d(&map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)a_pitch * 2, kBlockK, kBlockM);
   if (result != B200_OK) return result;

@@ -1,24 +1,23 @@
 // CSR SpMM  Y = A . X  (i32 indices, f32 values).
 //
-// One warp owns one output row; its 32 lanes cover 128 features with one float4
-// each, so a gathered row of X is one coalesced 512-byte read.  Column indices
-// and values are fetched 32 at a time (coalesced) and broadcast with shuffles.
-// Terms are added strictly in storage order with a separately rounded multiply
-// and add, so the result equals a sequential left-to-right evaluation bit for
-// bit.  Three kernels share that scheme:
-//   csr_spmm_bulk_kernel   X fits L2 (one launch): gathers are staged through
-//                          shared memory by the copy engine (cp.async.bulk),
-//                          224 KB in flight per SM, software-pipelined rows
-//   csr_spmm_block_kernel  X larger than L2: the call is cut into column blocks,
-//                          one launch each, accumulating into Y; gathers in
-//                          registers, many warps
-//   csr_spmm_kernel        any feature count / alignment (scalar fallback)
+// One warp owns one output row at a time; its 32 lanes cover 128 features with one float4
+// each, so a gathered row of X is one coalesced 512-byte read.  Terms are added strictly in
+// storage order with a separately rounded multiply and add, so the result equals a sequential
+// left-to-right evaluation bit for bit.  Kernels:
+//   csr_spmm_rows_kernel    16-byte aligned rows: persistent warps, one row ahead, the selected
+//                           terms of a row compacted in shared memory; an X larger than L2 is
+//                           processed in column blocks, one launch each, accumulating into Y
+//   csr_spmm_scalar_kernel  any feature count / alignment
+//   csr_spmv_kernel         a single feature
+//   gather_probe_kernel     measures the gather rate that bounds the above on this device
 // Algorithmic (compulsory) traffic per call: (rows+1)*4 + nnz*8 + columns*F*4 +
 // rows*F*4 bytes; the gathers touch nnz*F*4 bytes and are served by L2 where they hit.
 #include <stdlib.h>
 #include <string.h>
 
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -71,26 +70,21 @@ csr_spmm_scalar_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
 }
 
 // ---- per-call state and L2 eviction priorities --------------------------------
-// Words of the caller's int32 workspace (one per prepared call, zeroed once by the caller):
-//   [0] sticky: a bounded wait on a staged gather gave up   [1] the row that was left unwritten
-//   [2] "every row seen so far ascends": set by the first launch of a call, cleared by a
-//       launch that meets a descending row, read by the later launches of the same call.
+// Word of the caller's int32 workspace (one workspace per prepared call, zeroed once by the
+// caller) that carries "every row seen so far ascends" from the first launch of a call, which
+// sets it and clears it on meeting a descending row, to the later launches of the same call.
 // Nothing of a call lives in library-global device memory, so calls on different streams
-// cannot see one another's flags.
-constexpr int kStateTimeout = 0, kStateRow = 1, kStateSorted = 2;
+// cannot see one another's flag.  (Words 0 and 1 are the timeout report of the tensor-core
+// entries; this operator has no bounded wait and never writes them.)
+constexpr int kStateSorted = 2;
 
 __global__ void spmm_begin_kernel(int *state) { state[kStateSorted] = 1; }
 
 // X is gathered about 32 times per element while the index, value and Y streams are touched
-// once: gathers ask L2 to keep their lines (evict_last), the streams ask to be dropped first.
+// once: gathers ask L2 to keep their lines (evict_last) and skip L1, where they are never reused.
 __device__ __forceinline__ uint64_t policy_keep() {
   uint64_t policy;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-  return policy;
-}
-__device__ __forceinline__ uint64_t policy_stream() {
-  uint64_t policy;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
   return policy;
 }
 __device__ __forceinline__ float4 load_keep(const float *address, uint64_t policy) {
@@ -98,24 +92,6 @@ __device__ __forceinline__ float4 load_keep(const float *address, uint64_t polic
   asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(address), "l"(policy));
   return v;
-}
-template <typename T>
-__device__ __forceinline__ T load_stream(const T *address, uint64_t policy) {
-  uint32_t bits;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(bits) : "l"(address), "l"(policy));
-  T value;
-  memcpy(&value, &bits, 4);
-  return value;
-}
-__device__ __forceinline__ float4 load_stream4(const float *address, uint64_t policy) {
-  float4 v;
-  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(address), "l"(policy));
-  return v;
-}
-__device__ __forceinline__ void store_stream4(float *address, float4 v, uint64_t policy) {
-  asm volatile("st.global.L1::no_allocate.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
-               ::"l"(address), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(policy) : "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -148,302 +124,155 @@ __device__ __forceinline__ Block block_of_launch(const int *state, int column_lo
 }
 
 // ---------------------------------------------------------------------------
-// Staged gathers.  The gathers are latency-bound, so they are handed to the copy
-// engine instead of being held in registers: lane j of the warp that owns a row
-// issues ONE bulk asynchronous copy (cp.async.bulk, global -> shared, 512 bytes
-// for 128 features) for the j-th non-zero's row of X; the up-to-32 copies of a
-// batch complete on one mbarrier.  Every warp owns kStages staging buffers of
-// 32 x 512 bytes and requests batch i+1 while it folds batch i, so an SM keeps
-// kWarps x kStages x 16 KB (224 KB) of gathers in flight with no register cost.
-// The fold reads the staged rows back in storage order (lane l takes features
-// 4l..4l+3, conflict-free) and keeps the separately rounded multiply and add.
+// Persistent rows kernel.  What the profiler showed of a one-row-per-warp kernel with eight
+// gathers in flight per lane: the issue slots 66 % busy at 40 % occupancy, about 42 instructions
+// per gathered row of X, most of them spent finding the next selected non-zero (ballot,
+// find-first-set, two shuffles), on top of the offsets -> indices -> gathers chain.  Here
+//   * a warp owns rows w, w + W, w + 2W, ...; while it gathers for one row, the indices and
+//     values of the next row and the next row's partial sums are already requested, and row
+//     offsets are fetched 32 rows at a time, so the only round trips it waits for are gathers;
+//   * the non-zeros of a batch that fall into the launch's column block are compacted into
+//     shared memory once (offset of the X row in 16-byte units, value); the inner loop reads
+//     one broadcast pair per term, forms the address with one multiply-add and issues the load:
+//     about 15 instructions per gathered row, eight of them the unfused multiply and add;
+//   * gathers are issued kWindow at a time and the adds stay in storage order.  Measured on the
+//     262144 x 262144 / 32 per row / 128 feature case (two column blocks): windows of 2 and 4
+//     with four CTAs per SM take 365-380 us, windows of 8, 12, 16 take 450-700 us whatever the
+//     occupancy, and more than four CTAs per SM (fewer registers) is slower again.
 // ---------------------------------------------------------------------------
-constexpr int kBulkWarps = 7;
-constexpr int kBulkStages = 2;
-constexpr int kBulkRowBytes = 512;                       // 128 features
-constexpr int kBulkStageBytes = 32 * kBulkRowBytes;      // one batch of 32 non-zeros
-constexpr size_t kBulkSmemBytes = (size_t)kBulkWarps * kBulkStages * kBulkStageBytes + kBulkWarps * kBulkStages * 8 + 16;
-constexpr long long kBulkWaitCycles = 4000000000ll;      // ~2 s: a copy that has not landed by then never will
+constexpr int kRowsWarps = 8;
+constexpr int kRowsCtas = 4;    // CTAs per SM the kernel is compiled for (64 registers per thread)
+constexpr int kWindow = 4;      // gathers a lane issues before it folds them
 
-__device__ __forceinline__ uint32_t shared_address(const void *pointer) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
-}
-
-template <bool HINTS>
-__global__ void __launch_bounds__(kBulkWarps * 32, 1)
-csr_spmm_bulk_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
+template <bool ACCUMULATE>
+__global__ void __launch_bounds__(kRowsWarps * 32, kRowsCtas)
+csr_spmm_rows_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
                      const float *__restrict__ values, const float *__restrict__ dense,
-                     float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
-                     int64_t output_pitch, int column_lo, int column_hi, int phase, int *state) {
-  extern __shared__ __align__(128) unsigned char bulk_smem[];
-  const Block block = block_of_launch(state, column_lo, column_hi, phase);
-  if (block.skip) return;
+                     float *__restrict__ output, int rows, int features, uint32_t dense_pitch16,
+                     uint32_t output_pitch16, int column_lo, int column_hi, int phase, int *state) {
+  struct __align__(8) Term { uint32_t offset; float value; };   // offset of the X row in 16-byte units
+  __shared__ Term terms[kRowsWarps][32];
+  // ACCUMULATE is false only for launch 0, which never reads partial sums; a later launch decides here
+  // whether it accumulates its block or redoes the product (see block_of_launch).
   const bool check_order = phase == 0 && (column_lo != INT32_MIN || column_hi != INT32_MAX);
-  const uint64_t keep = policy_keep(), stream = policy_stream();
+  bool accumulate = ACCUMULATE;
+  if (ACCUMULATE) {
+    const Block block = block_of_launch(state, column_lo, column_hi, phase);
+    if (block.skip) return;
+    column_lo = block.lo; column_hi = block.hi; accumulate = block.accumulate;
+  }
+  const uint64_t keep = policy_keep();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int feature0 = blockIdx.y * 128;
-  const int width = min(128, features - feature0);         // features of this chunk
-  const uint32_t row_bytes = (uint32_t)width * 4;
-  const bool active = lane * 4 < width;
-  unsigned char *stage_base = bulk_smem + (size_t)warp * kBulkStages * kBulkStageBytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)kBulkWarps * kBulkStages * kBulkStageBytes) +
-                   warp * kBulkStages;
-  if (lane == 0) {
-    for (int s = 0; s < kBulkStages; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(bars + s)));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncwarp();
-
-  // This warp's rows are first_row, first_row + warps, ...; `count` of them.
-  const int64_t warps = (int64_t)gridDim.x * kBulkWarps;
-  const int64_t first_row = (int64_t)blockIdx.x * kBulkWarps + warp;
-  if (first_row >= rows) return;
-  const int64_t count = (rows - first_row + warps - 1) / warps;
-  const float *source = dense + feature0;
-
-  // A batch is up to 32 consecutive non-zeros of one row.  The walk over batches is a
-  // three-deep software pipeline, so no memory round trip sits on the critical path:
-  //   offsets   of 32 of this warp's rows at a time (lane k holds the k-th of them),
-  //   indices   (column, value) of the batch after the next one,
-  //   copies    of the next batch, while the current one is folded.
-  struct Cursor {
-    int64_t ordinal;   // which of this warp's rows
-    int base, stop;    // batch = non-zeros [base, min(base + 32, stop))
-  };
-  int cached_start = 0, cached_stop = 0;  // lane k: offsets of row ordinal (cache_block * 32 + k)
-  int64_t cache_block = -1;
-  auto offsets_of = [&](int64_t ordinal, int *start, int *stop) {
-    if (ordinal / 32 != cache_block) {
-      cache_block = ordinal / 32;
-      const int64_t mine = cache_block * 32 + lane;
-      cached_start = cached_stop = 0;
-      if (mine < count) {
-        const int64_t r = first_row + mine * warps;
-        cached_start = __ldg(row_offsets + r);
-        cached_stop = __ldg(row_offsets + r + 1);
-      }
-    }
-    *start = __shfl_sync(0xffffffffu, cached_start, (int)(ordinal % 32));
-    *stop = __shfl_sync(0xffffffffu, cached_stop, (int)(ordinal % 32));
-  };
-  struct Batch {
-    int column;        // lane j <-> j-th non-zero of the batch
-    float value;
-    int64_t row;       // -1: no batch (past the end)
-    int base, stop;
-    bool first, last;  // first / last batch of its row
-  };
-  auto advance = [&](Cursor &c) -> bool {   // false when the warp's rows are exhausted
-    if (c.base + 32 < c.stop) { c.base += 32; return true; }
-    if (++c.ordinal >= count) return false;
-    offsets_of(c.ordinal, &c.base, &c.stop);
-    return true;
-  };
-  int previous = INT32_MIN;                 // last column of the batch before, within one row
-  auto fetch = [&](const Cursor &c, bool valid, bool first) -> Batch {
-    Batch b;
-    b.row = valid ? first_row + c.ordinal * warps : -1;
-    b.base = c.base; b.stop = c.stop; b.first = first; b.last = c.base + 32 >= c.stop;
-    b.column = 0; b.value = 0.0f;
-    const bool stored = valid && c.base + lane < c.stop;
-    if (stored) {
-      if (HINTS) {
-        b.column = load_stream<int>(column_indices + c.base + lane, stream);
-        b.value = load_stream<float>(values + c.base + lane, stream);
-      } else {
-        b.column = __ldcs(column_indices + c.base + lane);
-        b.value = __ldcs(values + c.base + lane);
-      }
-    }
-    if (check_order && valid) {
-      if (first) previous = INT32_MIN;
-      const int before = __shfl_up_sync(0xffffffffu, b.column, 1);
-      const bool descends = stored && b.column < (lane == 0 ? previous : before);
-      if (__any_sync(0xffffffffu, descends) && lane == 0) state[kStateSorted] = 0;
-      previous = __shfl_sync(0xffffffffu, b.column, 31);
-    }
-    return b;
-  };
-  // Requests the gathers of one batch into `stage`; returns the lanes that take part.
-  auto request = [&](const Batch &b, int stage) -> unsigned {
-    const bool mine = b.row >= 0 && b.base + lane < b.stop && b.column >= block.lo && b.column < block.hi;
-    const unsigned mask = __ballot_sync(0xffffffffu, mine);
-    const uint32_t bar = shared_address(bars + stage);
-    if (lane == 0 && mask != 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(__popc(mask) * row_bytes)
-                   : "memory");
-    __syncwarp();
-    if (mine) {
-      const float *from = source + (int64_t)b.column * dense_pitch;
-      const uint32_t to = shared_address(stage_base + stage * kBulkStageBytes + lane * kBulkRowBytes);
-      if (HINTS)
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-                     ::"r"(to), "l"(from), "r"(row_bytes), "r"(bar), "l"(keep)
-                     : "memory");
-      else
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(to), "l"(from), "r"(row_bytes), "r"(bar)
-                     : "memory");
-    }
-    return mask;
-  };
-  auto try_wait = [&](int stage, uint32_t parity) -> bool {
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(shared_address(bars + stage)), "r"(parity) : "memory");
-    return done != 0;
-  };
-
-  Cursor cursor{0, 0, 0};
-  offsets_of(0, &cursor.base, &cursor.stop);
-  Batch current = fetch(cursor, true, true);
-  bool more = true;
-  bool crossed;
-  { const int64_t before = cursor.ordinal; more = advance(cursor); crossed = cursor.ordinal != before; }
-  Batch next = fetch(cursor, more, crossed);
-  uint32_t parity0 = 0, parity1 = 0;
-  int stage = 0;
-  unsigned current_mask = request(current, stage);
-  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  bool touched = false;
-  while (current.row >= 0) {
-    // indices of the batch after next, then the copies of the next batch
-    Batch after;
-    {
-      const int64_t before = cursor.ordinal;
-      if (more) more = advance(cursor);
-      after = fetch(cursor, more, cursor.ordinal != before);
-    }
-    const unsigned next_mask = request(next, stage ^ 1);
-
-    if (current.first) {
-      acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      touched = !block.accumulate;   // a launch that starts from zero always writes
-      if (block.accumulate && active) {  // partial sums of the earlier column blocks
-        const float *partial = output + current.row * output_pitch + feature0 + lane * 4;
-        acc = HINTS ? load_stream4(partial, stream) : __ldcs(reinterpret_cast<const float4 *>(partial));
-      }
-    }
-    if (current_mask != 0) {
-      touched = true;
-      const uint32_t parity = stage ? parity1 : parity0;
-      const long long begin = clock64();
-      bool landed = try_wait(stage, parity);
-      while (!landed && clock64() - begin < kBulkWaitCycles) landed = try_wait(stage, parity);
-      if (!landed) {  // give up: flag the failure, leave the row unwritten and stop this warp
-        if (lane == 0 && atomicCAS(&state[kStateTimeout], 0, 1) == 0) state[kStateRow] = (int)current.row;
-        if (next_mask != 0) {  // let the batch already requested land before the buffers go away
-          const long long drain = clock64();
-          const uint32_t other_parity = stage ? parity0 : parity1;
-          while (!try_wait(stage ^ 1, other_parity) && clock64() - drain < kBulkWaitCycles / 8) {}
-        }
-        return;
-      }
-      if (stage) parity1 ^= 1; else parity0 ^= 1;
-      const unsigned char *staged = stage_base + stage * kBulkStageBytes + lane * 16;
-#pragma unroll 8
-      for (int j = 0; j < 32; ++j) {
-        const float weight = __shfl_sync(0xffffffffu, current.value, j);
-        if (active && ((current_mask >> j) & 1u)) {
-          const float4 x = *reinterpret_cast<const float4 *>(staged + j * kBulkRowBytes);
-          acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x.x));
-          acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x.y));
-          acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x.z));
-          acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x.w));
-        }
-      }
-      __syncwarp();  // every lane has read the stage before it is requested again
-    }
-    if (current.last && active && touched) {
-      float *destination = output + current.row * output_pitch + feature0 + lane * 4;
-      if (HINTS) store_stream4(destination, acc, stream);
-      else __stcs(reinterpret_cast<float4 *>(destination), acc);
-    }
-    stage ^= 1;
-    current = next;
-    current_mask = next_mask;
-    next = after;
-  }
-  // No copy is left in flight here: every requested batch was waited for.
-}
-
-// Gathers held in registers (eight in flight per lane), one row per warp, many warps: the
-// alternative to staging for launches that see only a few non-zeros of every row.
-constexpr int kBlockWarps = 8;
-
-template <bool HINTS>
-__global__ void __launch_bounds__(kBlockWarps * 32)
-csr_spmm_block_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
-                      const float *__restrict__ values, const float *__restrict__ dense,
-                      float *__restrict__ output, int64_t rows, int features, int64_t dense_pitch,
-                      int64_t output_pitch, int column_lo, int column_hi, int phase, int *state) {
-  const Block block = block_of_launch(state, column_lo, column_hi, phase);
-  if (block.skip) return;
-  const uint64_t keep = policy_keep(), stream = policy_stream();
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kBlockWarps + (threadIdx.x >> 5);
+  const int stride = gridDim.x * kRowsWarps;
+  int row = blockIdx.x * kRowsWarps + warp;
   if (row >= rows) return;
-  const int feature = blockIdx.y * 128 + lane * 4;
-  const bool active = feature < features;
-  const int start = __ldg(row_offsets + row), stop = __ldg(row_offsets + row + 1);
-  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  float *destination = output + row * output_pitch + feature;
-  if (block.accumulate && active)
-    acc = HINTS ? load_stream4(destination, stream) : __ldcs(reinterpret_cast<const float4 *>(destination));
-  const float *source = dense + feature;
-  bool touched = !block.accumulate;  // a launch that starts from zero always writes
-  int previous = INT32_MIN;          // last column of the batch before (ascending check of launch 0)
-  for (int base = start; base < stop; base += 32) {
-    int column = 0;
-    float value = 0.0f;
-    bool mine = false;
-    if (base + lane < stop) {
-      if (HINTS) {
-        column = load_stream<int>(column_indices + base + lane, stream);
-        value = load_stream<float>(values + base + lane, stream);
-      } else {
-        column = __ldcs(column_indices + base + lane);
-        value = __ldcs(values + base + lane);
+  const int feature16 = blockIdx.y * 32 + lane;                 // this lane's 16-byte piece of a row
+  const bool active = feature16 * 4 < features;
+  const float4 *source = reinterpret_cast<const float4 *>(dense) + (active ? feature16 : 0);
+  float4 *result = reinterpret_cast<float4 *>(output) + (active ? feature16 : 0);
+  const unsigned below = (1u << lane) - 1u;
+  Term *mine_terms = terms[warp];
+
+  auto index_of = [&](int at) { return __ldcs(column_indices + at); };
+  auto value_of = [&](int at) { return __ldcs(values + at); };
+  auto partial_of = [&](int r) { return __ldcs(result + (uint64_t)r * output_pitch16); };
+  const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+
+  // Offsets of 32 of this warp's rows at a time: lane k holds those of the k-th row from `cached`.
+  int cached = row, cached_start = 0, cached_stop = 0;
+  auto refill = [&](int first) {
+    cached = first;
+    const int64_t mine = (int64_t)first + (int64_t)lane * stride;
+    cached_start = cached_stop = 0;
+    if (mine < rows) { cached_start = __ldg(row_offsets + mine); cached_stop = __ldg(row_offsets + mine + 1); }
+  };
+  refill(row);
+  int start = __shfl_sync(0xffffffffu, cached_start, 0), stop = __shfl_sync(0xffffffffu, cached_stop, 0);
+  int column = 0, next_column = 0;
+  float value = 0.0f, next_value = 0.0f;
+  if (start + lane < stop) { column = index_of(start + lane); value = value_of(start + lane); }
+  float4 acc = ACCUMULATE && accumulate && active ? partial_of(row) : zero, next_acc = zero;
+  int ordinal = 0;                                   // of `row` within the cached block of 32
+
+  for (; row < rows; row += stride) {
+    // requests for the next row, before this row's gathers
+    int next_start = 0, next_stop = 0;
+    const int64_t next_row = (int64_t)row + stride;
+    if (next_row < rows) {
+      if (++ordinal == 32) { refill((int)next_row); ordinal = 0; }
+      next_start = __shfl_sync(0xffffffffu, cached_start, ordinal);
+      next_stop = __shfl_sync(0xffffffffu, cached_stop, ordinal);
+      next_column = 0; next_value = 0.0f;
+      if (next_start + lane < next_stop) { next_column = index_of(next_start + lane); next_value = value_of(next_start + lane); }
+      if (ACCUMULATE && accumulate && active) next_acc = partial_of((int)next_row);
+    }
+    bool touched = !accumulate;        // a launch that starts from zero always writes
+    int previous = INT32_MIN;          // last column of the batch before (ascending check of launch 0)
+    for (int base = start; base < stop; base += 32) {
+      if (base != start) {             // rows longer than one batch fetch their later batches in place
+        column = 0; value = 0.0f;
+        if (base + lane < stop) { column = index_of(base + lane); value = value_of(base + lane); }
       }
-      mine = column >= block.lo && column < block.hi;
-    }
-    if (phase == 0) {
-      const int before = __shfl_up_sync(0xffffffffu, column, 1);
-      const bool descends = base + lane < stop && column < (lane == 0 ? previous : before);
-      if (__any_sync(0xffffffffu, descends) && lane == 0) state[kStateSorted] = 0;
-      previous = __shfl_sync(0xffffffffu, column, 31);
-    }
-    unsigned mask = __ballot_sync(0xffffffffu, mine);
-    touched |= mask != 0;
-    while (mask != 0) {  // eight gathers at a time, in storage order
-      int lanes[8];
-      float4 gathered[8];
+      const bool stored = base + lane < stop;
+      if (check_order) {
+        const int before = __shfl_up_sync(0xffffffffu, column, 1);
+        const bool descends = stored && column < (lane == 0 ? previous : before);
+        if (__any_sync(0xffffffffu, descends) && lane == 0) state[kStateSorted] = 0;
+        previous = __shfl_sync(0xffffffffu, column, 31);
+      }
+      const bool selected = stored && column >= column_lo && column < column_hi;
+      const unsigned mask = __ballot_sync(0xffffffffu, selected);
+      if (mask == 0) continue;
+      touched = true;
+      if (selected) mine_terms[__popc(mask & below)] = Term{(uint32_t)column * dense_pitch16, value};
+      __syncwarp();
+      const int count = __popc(mask);
+      int j = 0;
+      for (; j + kWindow <= count; j += kWindow) {   // full windows: no per-term predicate
+        float4 x[kWindow];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        lanes[u] = mask ? __ffs(mask) - 1 : -1;
-        if (mask) mask &= mask - 1;
-        const int c = __shfl_sync(0xffffffffu, column, lanes[u] < 0 ? 0 : lanes[u]);
-        if (active && lanes[u] >= 0) {
-          const float *from = source + (int64_t)c * dense_pitch;
-          gathered[u] = HINTS ? load_keep(from, keep) : __ldg(reinterpret_cast<const float4 *>(from));
+        for (int u = 0; u < kWindow; ++u) {
+          const float4 *from = source + mine_terms[j + u].offset;
+          x[u] = load_keep(reinterpret_cast<const float *>(from), keep);
+        }
+#pragma unroll
+        for (int u = 0; u < kWindow; ++u) {
+          const float weight = mine_terms[j + u].value;
+          acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x[u].x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x[u].y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x[u].z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x[u].w));
         }
       }
+      if (j < count) {                                // the last, partial window
+        float4 x[kWindow];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float weight = __shfl_sync(0xffffffffu, value, lanes[u] < 0 ? 0 : lanes[u]);
-        if (active && lanes[u] >= 0) {
-          acc.x = __fadd_rn(acc.x, __fmul_rn(weight, gathered[u].x));
-          acc.y = __fadd_rn(acc.y, __fmul_rn(weight, gathered[u].y));
-          acc.z = __fadd_rn(acc.z, __fmul_rn(weight, gathered[u].z));
-          acc.w = __fadd_rn(acc.w, __fmul_rn(weight, gathered[u].w));
+        for (int u = 0; u < kWindow; ++u) {
+          if (j + u < count) {
+            const float4 *from = source + mine_terms[j + u].offset;
+            x[u] = load_keep(reinterpret_cast<const float *>(from), keep);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kWindow; ++u) {
+          if (j + u < count) {
+            const float weight = mine_terms[j + u].value;
+            acc.x = __fadd_rn(acc.x, __fmul_rn(weight, x[u].x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(weight, x[u].y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(weight, x[u].z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(weight, x[u].w));
+          }
         }
       }
+      __syncwarp();                                   // every lane has read the terms before the next batch overwrites them
     }
-  }
-  if (active && touched) {
-    if (HINTS) store_stream4(destination, acc, stream);
-    else __stcs(reinterpret_cast<float4 *>(destination), acc);
+    if (active && touched) {
+      float4 *destination = result + (uint64_t)row * output_pitch16;
+      __stcs(destination, acc);
+    }
+    start = next_start; stop = next_stop;
+    column = next_column; value = next_value;
+    acc = next_acc;
   }
 }
 
@@ -461,92 +290,22 @@ gather_probe_kernel(const float *__restrict__ table, int64_t table_rows, int64_t
   const uint64_t keep = policy_keep();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  uint64_t position = (uint64_t)(warp + 1) * 0x9E3779B97F4A7C15ull;
+  uint32_t position = (uint32_t)(warp + 1) * 2654435761u;
+  const float4 *source = reinterpret_cast<const float4 *>(table) + lane;
   float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (int64_t done = 0; done < per_warp; done += DEPTH) {
     float4 got[DEPTH];
 #pragma unroll
     for (int d = 0; d < DEPTH; ++d) {
-      position = position * 6364136223846793005ull + 1442695040888963407ull;
-      const int64_t row = (int64_t)((position >> 33) % (uint64_t)table_rows);
-      const float *from = table + row * 128 + lane * 4;
-      got[d] = HINTS ? load_keep(from, keep) : __ldg(reinterpret_cast<const float4 *>(from));
+      position = position * 1664525u + 1013904223u;
+      const uint32_t row = __umulhi(position, (uint32_t)table_rows);   // uniform in [0, table_rows)
+      const float4 *from = source + row * 32u;
+      got[d] = HINTS ? load_keep(reinterpret_cast<const float *>(from), keep) : __ldg(from);
     }
 #pragma unroll
     for (int d = 0; d < DEPTH; ++d) { acc.x += got[d].x; acc.y += got[d].y; acc.z += got[d].z; acc.w += got[d].w; }
   }
   if (acc.x == 12345.678f) sink[warp * 128 + lane * 4] = acc.y + acc.z + acc.w;  // never true in practice
-}
-
-// The same walk with the copy engine: every lane requests one 512-byte row into the warp's
-// staging buffer (two stages of 32 rows), as the staged SpMM kernel does.
-template <bool HINTS>
-__global__ void __launch_bounds__(kBulkWarps * 32, 1)
-gather_probe_bulk_kernel(const float *__restrict__ table, int64_t table_rows, int64_t per_warp, float *__restrict__ sink,
-                         int *state) {
-  extern __shared__ __align__(128) unsigned char bulk_smem[];
-  const uint64_t keep = policy_keep();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned char *stage_base = bulk_smem + (size_t)warp * kBulkStages * kBulkStageBytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)kBulkWarps * kBulkStages * kBulkStageBytes) +
-                   warp * kBulkStages;
-  if (lane == 0) {
-    for (int s = 0; s < kBulkStages; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(bars + s)));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncwarp();
-  const int64_t global_warp = (int64_t)blockIdx.x * kBulkWarps + warp;
-  uint64_t position = (uint64_t)(global_warp * 32 + lane + 1) * 0x9E3779B97F4A7C15ull;
-  auto request = [&](int stage) {
-    const uint32_t bar = shared_address(bars + stage);
-    if (lane == 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(32 * kBulkRowBytes) : "memory");
-    __syncwarp();
-    position = position * 6364136223846793005ull + 1442695040888963407ull;
-    const float *from = table + (int64_t)((position >> 33) % (uint64_t)table_rows) * 128;
-    const uint32_t to = shared_address(stage_base + stage * kBulkStageBytes + lane * kBulkRowBytes);
-    if (HINTS)
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-                   ::"r"(to), "l"(from), "r"(kBulkRowBytes), "r"(bar), "l"(keep) : "memory");
-    else
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(to), "l"(from), "r"(kBulkRowBytes), "r"(bar) : "memory");
-  };
-  auto try_wait = [&](int stage, uint32_t parity) -> bool {
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(shared_address(bars + stage)), "r"(parity) : "memory");
-    return done != 0;
-  };
-  const int64_t batches = (per_warp + 31) / 32;
-  uint32_t parity[2] = {0, 0};
-  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  request(0);
-  for (int64_t batch = 0; batch < batches; ++batch) {
-    const int stage = (int)(batch & 1);
-    if (batch + 1 < batches) request(stage ^ 1);
-    const long long begin = clock64();
-    bool landed = try_wait(stage, parity[stage]);
-    while (!landed && clock64() - begin < kBulkWaitCycles) landed = try_wait(stage, parity[stage]);
-    if (!landed) {
-      if (lane == 0 && atomicCAS(&state[kStateTimeout], 0, 1) == 0) state[kStateRow] = (int)batch;
-      if (batch + 1 < batches) {
-        const long long drain = clock64();
-        while (!try_wait(stage ^ 1, parity[stage ^ 1]) && clock64() - drain < kBulkWaitCycles / 8) {}
-      }
-      return;
-    }
-    parity[stage] ^= 1;
-    const unsigned char *staged = stage_base + stage * kBulkStageBytes + lane * 16;
-#pragma unroll 8
-    for (int j = 0; j < 32; ++j) {
-      const float4 x = *reinterpret_cast<const float4 *>(staged + j * kBulkRowBytes);
-      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-    }
-    __syncwarp();
-  }
-  if (acc.x == 12345.678f) sink[global_warp * 128 + lane * 4] = acc.y + acc.z + acc.w;
 }
 
 // CSR SpMV  y = A . x  (csr_spmm with a single feature).  A warp takes kSpmvRows consecutive rows.
@@ -598,12 +357,23 @@ csr_spmv_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restri
 // Number of column blocks: X is cut into slices of at most kBlockBytes so that a slice
 // stays resident in L2 (126 MB, shared with the streamed index, value and Y traffic).
 constexpr int64_t kBlockBytes = 72ll << 20;
-constexpr bool kColumnBlocksStaged = false;   // column blocks run on the register kernel unless overridden
+// CTAs of `kernel` one SM holds (registers decide), per device and kernel.
+int resident_blocks(const void *kernel, int threads) {
+  static std::mutex lock;
+  static std::map<std::pair<const void *, int>, int> known;
+  int device = 0;
+  cudaGetDevice(&device);
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = known.find({kernel, device});
+  if (found != known.end()) return found->second;
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, 0) != cudaSuccess || blocks < 1) blocks = 1;
+  known[{kernel, device}] = blocks;
+  return blocks;
+}
 
-// Tuning overrides, read at every call so that one process can sweep them:
-//   INTENT_B200_SPMM_PHASES  1..16   number of column blocks
-//   INTENT_B200_SPMM_KERNEL  staged | registers   which kernel runs the column blocks
-//   INTENT_B200_SPMM_HINTS   0 | 1   L2 eviction priorities on the loads and stores
+// INTENT_B200_SPMM_PHASES (1..16) overrides the number of column blocks; it is read at every
+// call so that one process can sweep it (and tests can force the blocked path on small inputs).
 int tuning_integer(const char *name, int low, int high, int otherwise) {
   const char *text = getenv(name);
   const int value = text ? atoi(text) : otherwise;
@@ -666,7 +436,10 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
   int *state = static_cast<int *>(workspace);
   const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
   if (ctas > INT32_MAX) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "csr_spmm: too many rows");
-  const bool vector = x_d1 % 4 == 0 && x_s0 % 4 == 0 && y_s0 % 4 == 0 && aligned16(dense) && aligned16(output);
+  // vector path: 16-byte aligned rows whose offsets (in 16-byte units) fit 32 bits
+  const bool vector = x_d1 % 4 == 0 && x_s0 % 4 == 0 && y_s0 % 4 == 0 && aligned16(dense) && aligned16(output) &&
+                      (x_d0 == 0 || (x_d0 - 1) * (x_s0 / 4) + (x_d1 + 3) / 4 <= (int64_t)UINT32_MAX) &&
+                      x_s0 / 4 <= (int64_t)UINT32_MAX && y_s0 / 4 <= (int64_t)UINT32_MAX && rows <= INT32_MAX - 64 * 1024 * 1024;
   if (!vector) {
     csr_spmm_scalar_kernel<<<(unsigned)ctas, kWarpsPerCta * 32, 0, s>>>(
         (const int32_t *)row_offsets, (const int32_t *)column_indices, (const float *)values,
@@ -675,61 +448,39 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
     return B200_OK;
   }
   const int phases = column_phases(x_d0, x_d1);
-  const bool hints = tuning_integer("INTENT_B200_SPMM_HINTS", 0, 1, 1) != 0;
-  const char *choice = getenv("INTENT_B200_SPMM_KERNEL");
-  const bool staged = phases == 1 || (choice ? strcmp(choice, "staged") == 0 : kColumnBlocksStaged);
   const unsigned chunks = (unsigned)((x_d1 + 127) / 128);
-  if (staged) {
-    B200_CUDA_TRY(opt_in_dynamic_smem(csr_spmm_bulk_kernel<true>, kBulkSmemBytes));
-    B200_CUDA_TRY(opt_in_dynamic_smem(csr_spmm_bulk_kernel<false>, kBulkSmemBytes));
-  }
   if (phases > 1) spmm_begin_kernel<<<1, 1, 0, s>>>(state);
-  const int64_t wanted = (rows + kBulkWarps - 1) / kBulkWarps;
-  const int64_t resident = sm_count();
-  const dim3 staged_grid((unsigned)(wanted < resident ? wanted : resident), chunks);
-  const dim3 register_grid((unsigned)((rows + kBlockWarps - 1) / kBlockWarps), chunks);
   const int64_t span = (x_d0 + phases - 1) / phases;
   for (int phase = 0; phase < phases; ++phase) {
     const int lo = phases > 1 ? (int)(phase * span) : INT32_MIN;
     const int hi = phases > 1 && phase + 1 < phases ? (int)((phase + 1) * span) : INT32_MAX;
-    auto launch = [&](auto kernel, dim3 grid, int threads, size_t smem) {
-      kernel<<<grid, threads, smem, s>>>((const int32_t *)row_offsets, (const int32_t *)column_indices,
-                                         (const float *)values, (const float *)dense, (float *)output, rows,
-                                         (int)x_d1, x_s0, y_s0, lo, hi, phase, state);
+    auto launch = [&](auto kernel) {
+      const int per_sm = resident_blocks(reinterpret_cast<const void *>(kernel), kRowsWarps * 32);
+      const int64_t wanted = (rows + kRowsWarps - 1) / kRowsWarps, resident = (int64_t)sm_count() * per_sm;
+      const dim3 grid((unsigned)(wanted < resident ? wanted : resident), chunks);
+      kernel<<<grid, kRowsWarps * 32, 0, s>>>((const int32_t *)row_offsets, (const int32_t *)column_indices,
+                                               (const float *)values, (const float *)dense, (float *)output, (int)rows,
+                                               (int)x_d1, (uint32_t)(x_s0 / 4), (uint32_t)(y_s0 / 4), lo, hi, phase, state);
     };
-    if (staged) {
-      if (hints) launch(csr_spmm_bulk_kernel<true>, staged_grid, kBulkWarps * 32, kBulkSmemBytes);
-      else launch(csr_spmm_bulk_kernel<false>, staged_grid, kBulkWarps * 32, kBulkSmemBytes);
-    } else {
-      if (hints) launch(csr_spmm_block_kernel<true>, register_grid, kBlockWarps * 32, 0);
-      else launch(csr_spmm_block_kernel<false>, register_grid, kBlockWarps * 32, 0);
-    }
+    if (phase == 0) launch(csr_spmm_rows_kernel<false>);
+    else launch(csr_spmm_rows_kernel<true>);
   }
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
-// Gather-rate probe (see gather_probe_kernel).  `variant`: 0..3 = 4, 8, 16, 32 register loads
-// in flight per lane; 4 = staged through shared memory by the copy engine.  `hints` selects
-// the evict_last priority on the gathers.  Reads table_rows x 512 bytes; writes nothing.
+// Gather-rate probe (see gather_probe_kernel).  `variant`: 0..3 = 4, 8, 16, 32 loads in flight
+// per lane.  `hints` selects the evict_last priority on the gathers.  Writes nothing.
 extern "C" int b200_gather_probe(const void *table, int64_t table_rows, int64_t gathers, int32_t variant,
                                  int32_t hints, void *sink, void *workspace, void *stream) {
-  if (!table || !sink || !workspace || table_rows < 1 || gathers < 1 || variant < 0 || variant > 4)
+  if (!table || !sink || !workspace || table_rows < 1 || table_rows > (1 << 26) || gathers < 1 || variant < 0 ||
+      variant > 3)
     return fail(B200_ERR_INVALID_ARGUMENT, "gather_probe: bad arguments");
   if (!aligned16(table)) return fail(B200_ERR_UNSUPPORTED_LAYOUT, "gather_probe: table must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float *t = static_cast<const float *>(table);
   float *out = static_cast<float *>(sink);
-  if (variant == 4) {
-    const int64_t warps = (int64_t)sm_count() * kBulkWarps;
-    const int64_t per_warp = (gathers + warps - 1) / warps;
-    B200_CUDA_TRY(opt_in_dynamic_smem(gather_probe_bulk_kernel<true>, kBulkSmemBytes));
-    B200_CUDA_TRY(opt_in_dynamic_smem(gather_probe_bulk_kernel<false>, kBulkSmemBytes));
-    if (hints)
-      gather_probe_bulk_kernel<true><<<sm_count(), kBulkWarps * 32, kBulkSmemBytes, s>>>(t, table_rows, per_warp, out, (int *)workspace);
-    else
-      gather_probe_bulk_kernel<false><<<sm_count(), kBulkWarps * 32, kBulkSmemBytes, s>>>(t, table_rows, per_warp, out, (int *)workspace);
-  } else {
+  {
     const int64_t ctas = (int64_t)sm_count() * 8;          // 64 warps per SM
     const int64_t per_warp = (gathers + ctas * 8 - 1) / (ctas * 8);
 #define B200_PROBE(D) \
@@ -771,20 +522,6 @@ extern "C" int b200_csr_validate(const void *row_offsets, int64_t rows, const vo
     if (where) *where = position;
     return fail(B200_ERR_INVALID_ARGUMENT, "csr_validate: %s[%lld] is out of range",
                 host <= (unsigned long long)rows ? "row_offsets" : "column_indices", (long long)position);
-  }
-  return B200_OK;
-}
-
-extern "C" int b200_csr_spmm_status(const void *workspace, int64_t *row, void *stream) {
-  if (!workspace) return fail(B200_ERR_INVALID_ARGUMENT, "csr_spmm_status: null workspace");
-  int words[2] = {0, 0};
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B200_CUDA_TRY(cudaMemcpyAsync(words, workspace, sizeof words, cudaMemcpyDeviceToHost, s));
-  B200_CUDA_TRY(cudaStreamSynchronize(s));
-  if (row) *row = words[1];
-  if (words[0] != 0) {
-    cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof words, s);   // the report is delivered once
-    return fail(B200_ERR_DEVICE_TIMEOUT, "csr_spmm: a staged gather did not arrive (row %d left unwritten)", words[1]);
   }
   return B200_OK;
 }

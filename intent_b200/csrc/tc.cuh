@@ -220,6 +220,67 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
                ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) ------------------------------------------------
+// Two CTAs of a cluster on the two SMs of a TPC issue ONE MMA over a 256-row tile: each CTA
+// holds its 128 rows of A, its half of B's N columns and its 128 lanes of the accumulator; the
+// even CTA (rank 0, the "leader") issues for both.  Each CTA loads its own halves with plain
+// (unicast) TMA copies whose completion bytes are counted on the LEADER's barrier; commits
+// arrive on the barrier at the same shared-memory offset in both CTAs.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// Every thread of every CTA of the cluster; also orders shared-memory accesses across the pair.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `smem_address` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_address(uint32_t smem_address, uint32_t rank) {
+  uint32_t mapped;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(mapped) : "r"(smem_address), "r"(rank));
+  return mapped;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void store_cluster_u32(uint32_t cluster_word, uint32_t value) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_word), "r"(value) : "memory");
+}
+// 2-D tiled load into THIS CTA's shared memory; the bytes complete on `cluster_bar`, a barrier
+// of the pair's leader given as a cluster address.  Unicast: every CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map, uint32_t cluster_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+// Whole-warp, issued by the same warp of BOTH CTAs with the same shared-memory slot offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *slot_in_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_u32(slot_in_smem)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+// D[tmem of both CTAs] (+)= A . B over the pair; issued by one thread of the leader.
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive, once the pair's MMAs issued so far have completed, on the barrier at `bar`'s offset in
+// every CTA of `cta_mask` (bit i = CTA rank i).  This is a barrier arrival, not a data copy.
+__device__ __forceinline__ void mma_commit_pair(uint64_t *bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane
 // (base lane + i), columns [column, column + 32).
 __device__ __forceinline__ void tmem_load_32x32(uint32_t address, uint32_t (&r)[32]) {

@@ -186,18 +186,7 @@ def attention_backward_dq(q, k, v, grad_output, lse, delta, scale: float, *, hea
     return grad_q
 
 
-def csr_spmm_status(device, state=None) -> None:
-    """Synchronise and raise if a bounded wait inside csr_spmm gave up."""
-    device = torch.device(device)
-    state = workspace(device) if state is None else state
-    row = ctypes.c_int64(-1)
-    with torch.cuda.device(device):
-        status = _native.entry("b200_csr_spmm_status")(state.data_ptr(), ctypes.byref(row),
-                                                        torch.cuda.current_stream(device).cuda_stream)
-    _native.check("b200_csr_spmm_status", status)
-
-
-def gather_probe(table: torch.Tensor, gathers: int, *, variant: int = 4, hints: bool = True) -> None:
+def gather_probe(table: torch.Tensor, gathers: int, *, variant: int = 1, hints: bool = True) -> None:
     """Enqueues the gather-rate probe over `table` (rows of 128 f32)."""
     device = _require_cuda(table)
     if table.dtype != torch.float32 or table.dim() != 2 or table.shape[1] != 128 or not table.is_contiguous():

@@ -141,7 +141,9 @@ def test_prepared_sequence_and_host_buffers_of_the_reference(intent):
     x, w, b, inv, eps = workloads.layer_norm_inputs(64, 1024, seed=16)
     buffers = HostBuffers("b200", DEV)
     buffers.begin()
-    staged = [buffers.input(t.numpy(), element="f16") for t in (x, w, b)]
+    import numpy
+    # NumPy arrays are what the scope stages (it passes torch tensors through as native storage)
+    staged = [buffers.input(numpy.array(t.numpy()), element="f16") for t in (x, w, b)]
     assert all(t.device.type == "cuda" for t in staged)
     norm = intent.jit(layer_norm_f16, backend="b200")
     soft = intent.jit(stable_softmax_f16, backend="b200")
@@ -157,7 +159,7 @@ def test_prepared_sequence_and_host_buffers_of_the_reference(intent):
     assert len(sequence.observations) == 2
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
-    sequence.enqueue(stream) if hasattr(sequence, "enqueue") else sequence.launch()
+    sequence.enqueue(stream)
     stream.synchronize()
     assert relative_error(sequence.result(), expected) <= 1e-2
     buffers.close()
