@@ -7,8 +7,6 @@
 // several warps, one named barrier per reduction.  Row groups stride over the
 // rows (persistent grid sized from the SM count) so LayerNorm's gamma/beta are
 // staged in shared memory once per CTA.
-#include <stdlib.h>
-
 #include <mutex>
 
 #include "common.cuh"
@@ -95,79 +93,6 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
     }
     if (WARPS > 1)  // scratch is reused by the next row of this group
       asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(kRowThreads) : "memory");
-  }
-}
-
-// One warp per row, several rows per warp, one row ahead: the raw vectors of the warp's next
-// row are requested before the current row is reduced, and the current row's stores are issued
-// while those loads are in flight.  With a single row per warp every warp of the grid loads,
-// then computes, then stores in step with all the others, so the read burst and the write burst
-// of the whole matrix never overlap; here they do.
-template <typename T, int ITERS, int CTA_WARPS>
-__global__ void __launch_bounds__(CTA_WARPS * 32)
-softmax_rows_ahead_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int columns,
-                          int64_t x_pitch, int64_t y_pitch) {
-  constexpr int kVec = Element<T>::kVec;
-  const int lane = threadIdx.x & 31;
-  const int64_t stride = (int64_t)gridDim.x * CTA_WARPS;
-  int64_t row = (int64_t)blockIdx.x * CTA_WARPS + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  uint4 ahead[ITERS];
-  auto request = [&](int64_t r) {
-    const T *source = x + r * x_pitch;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int column = (it * 32 + lane) * kVec;
-      if (column < columns) ahead[it] = __ldcs(reinterpret_cast<const uint4 *>(source + column));
-    }
-  };
-  request(row);
-  for (; row < rows; row += stride) {
-    float value[ITERS][kVec];
-    float maximum = -INFINITY;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int column = (it * 32 + lane) * kVec;
-      if (column < columns) {
-        const T *lanes = reinterpret_cast<const T *>(&ahead[it]);
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) {
-          value[it][i] = Element<T>::widen(lanes[i]);
-          maximum = maximum_num(maximum, value[it][i]);
-        }
-      }
-    }
-    if (row + stride < rows) request(row + stride);
-    maximum = warp_max(maximum);
-    float sum = 0.0f;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int column = (it * 32 + lane) * kVec;
-      if (column < columns) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) {
-          value[it][i] = expf(value[it][i] - maximum);
-          sum += value[it][i];
-        }
-      }
-    }
-    sum = warp_sum(sum);
-    T *destination = y + row * y_pitch;
-    const float inverse = __fdiv_rn(1.0f, sum);  // f32 kernel: multiply by the reciprocal
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int column = (it * 32 + lane) * kVec;
-      if (column < columns) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i)
-          value[it][i] = sizeof(T) == 4 ? __fmul_rn(value[it][i], inverse) : __fdiv_rn(value[it][i], sum);
-        uint4 raw;
-        T *lanes = reinterpret_cast<T *>(&raw);
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) lanes[i] = Element<T>::narrow(value[it][i]);
-        __stcs(reinterpret_cast<uint4 *>(destination + column), raw);
-      }
-    }
   }
 }
 
@@ -482,34 +407,10 @@ int grid_for(int64_t rows, int groups_per_cta, int ctas_per_sm) {
   return (int)(wanted < resident ? wanted : resident);
 }
 
-// Rows each warp of the one-row-ahead kernel walks; 0 selects the one-row-per-warp kernel.
-// INTENT_B200_SOFTMAX_ROWS_PER_WARP overrides it (read at every call).
-constexpr int kSoftmaxRowsPerWarp = 0;
-int softmax_rows_per_warp() {
-  const char *text = getenv("INTENT_B200_SOFTMAX_ROWS_PER_WARP");
-  const int value = text ? atoi(text) : kSoftmaxRowsPerWarp;
-  return value >= 0 && value <= 64 ? value : kSoftmaxRowsPerWarp;
-}
-
 template <typename T, int WARPS, int ITERS>
 int launch_softmax_rows(const T *x, T *y, int64_t rows, int64_t columns, int64_t xp, int64_t yp,
                         cudaStream_t stream) {
   using Shape = SoftmaxShape<WARPS>;
-  const int per_warp = WARPS == 1 ? softmax_rows_per_warp() : 0;
-  if (per_warp >= 1 && rows >= (int64_t)per_warp * kSoftmaxCtaWarps * sm_count()) {
-    const int64_t warps = (rows + per_warp - 1) / (per_warp > 0 ? per_warp : 1);
-    const char *text = getenv("INTENT_B200_SOFTMAX_CTA_WARPS");
-    const int cta_warps = text ? atoi(text) : 4;
-    auto run = [&](auto kernel, int w) {
-      kernel<<<(unsigned)((warps + w - 1) / w), w * 32, 0, stream>>>(x, y, rows, (int)columns, xp, yp);
-    };
-    if (cta_warps >= 28) run(softmax_rows_ahead_kernel<T, ITERS, 28>, 28);
-    else if (cta_warps >= 16) run(softmax_rows_ahead_kernel<T, ITERS, 16>, 16);
-    else if (cta_warps >= 8) run(softmax_rows_ahead_kernel<T, ITERS, 8>, 8);
-    else run(softmax_rows_ahead_kernel<T, ITERS, 4>, 4);
-    B200_CUDA_TRY(cudaGetLastError());
-    return B200_OK;
-  }
   const int grid = grid_for(rows, Shape::kGroups,
                             resident_ctas(softmax_rows_kernel<T, WARPS, ITERS>, Shape::kCtaThreads, 0));
   softmax_rows_kernel<T, WARPS, ITERS><<<grid, Shape::kCtaThreads, 0, stream>>>(

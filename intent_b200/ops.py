@@ -41,6 +41,23 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     return device
 
 
+def _expect(name: str, tensor: torch.Tensor, dtype: torch.dtype, shape=None) -> None:
+    """What the runtime binder checks for a bound view (``B200Program._observe``), for callers
+    that come straight here: a wrong element type or extent must never reach the kernel, which
+    trusts them (an int64 index array read as int32, or an output buffer of half the size, would
+    send loads and stores out of bounds)."""
+    if tensor.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {tensor.dtype}")
+    if shape is not None and tuple(tensor.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(tensor.shape)}")
+
+
+def _float_type(name: str, tensor: torch.Tensor, allowed=(torch.float32, torch.float16, torch.bfloat16)) -> torch.dtype:
+    if tensor.dtype not in allowed:
+        raise TypeError(f"{name} must be one of {', '.join(str(d) for d in allowed)}, got {tensor.dtype}")
+    return tensor.dtype
+
+
 def _call(name: str, device: torch.device, *arguments) -> None:
     with torch.cuda.device(device):
         _native.check(name, _native.entry(name)(*arguments))
@@ -69,15 +86,25 @@ def workspace_status(device: torch.device) -> None:
 
 
 def softmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    device = _require_cuda(x)
+    device = _require_cuda(x) if out is None else _require_cuda(x, out)
+    _float_type("x", x)
+    if x.dim() != 2:
+        raise ValueError("softmax takes a matrix")
     y = torch.empty(x.shape, dtype=x.dtype, device=device) if out is None else out
+    _expect("out", y, x.dtype, x.shape)
     _call("b200_softmax", device, *_slots(x), *_slots(y), _CODES[x.dtype], _stream(x))
     return y
 
 
 def layer_norm(x, weight, bias, inverse_features: float, epsilon: float, out=None, *, centered=None):
-    device = _require_cuda(x, weight, bias)
+    device = _require_cuda(x, weight, bias) if out is None else _require_cuda(x, weight, bias, out)
+    _float_type("x", x)
+    if x.dim() != 2:
+        raise ValueError("layer_norm takes a matrix")
+    _expect("weight", weight, x.dtype, (x.shape[1],))
+    _expect("bias", bias, x.dtype, (x.shape[1],))
     y = torch.empty(x.shape, dtype=x.dtype, device=device) if out is None else out
+    _expect("out", y, x.dtype, x.shape)
     if centered is None:  # the f32 kernel of the reference is the uncentred one
         centered = x.dtype != torch.float32
     _call("b200_layer_norm", device, *_slots(x), *_slots(weight), *_slots(bias), *_slots(y),
@@ -86,47 +113,81 @@ def layer_norm(x, weight, bias, inverse_features: float, epsilon: float, out=Non
 
 
 def gemm(a, b, out=None, *, relu: bool = False):
-    device = _require_cuda(a, b)
+    device = _require_cuda(a, b) if out is None else _require_cuda(a, b, out)
+    _float_type("a", a, (torch.float16, torch.bfloat16))
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("gemm takes two matrices")
+    _expect("b", b, a.dtype, (a.shape[1], b.shape[1]))
     c = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device) if out is None else out
+    _expect("out", c, a.dtype, (a.shape[0], b.shape[1]))
     _call("b200_gemm", device, *_slots(a), *_slots(b), *_slots(c), *_slots(workspace(device)),
           _CODES[a.dtype], int(relu), _stream(a))
     return c
 
 
 def flash_attention(q, k, v, scale: float, out=None, *, head_group: int = 1, causal: bool = True):
-    device = _require_cuda(q, k, v)
+    device = _require_cuda(q, k, v) if out is None else _require_cuda(q, k, v, out)
+    _float_type("q", q, (torch.float16, torch.bfloat16))
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("flash_attention takes (batch, heads, sequence, head_dim) tensors")
+    _expect("k", k, q.dtype, (q.shape[0], k.shape[1], k.shape[2], q.shape[3]))
+    _expect("v", v, q.dtype, (q.shape[0], k.shape[1], k.shape[2], v.shape[3]))
     if out is None:
         out = torch.empty((*q.shape[:3], v.shape[3]), dtype=q.dtype, device=device)
+    _expect("out", out, q.dtype, (*q.shape[:3], v.shape[3]))
     _call("b200_flash_attention", device, *_slots(q), *_slots(k), *_slots(v), *_slots(out),
           float(scale), *_slots(workspace(device)), _CODES[q.dtype], int(head_group), int(causal),
           _stream(q))
     return out
 
 
+def _csr_operands(row_offsets, column_indices, values) -> None:
+    _expect("row_offsets", row_offsets, torch.int32)
+    _expect("column_indices", column_indices, torch.int32)
+    _expect("values", values, torch.float32, column_indices.shape)
+    if row_offsets.dim() != 1 or column_indices.dim() != 1 or row_offsets.numel() < 1:
+        raise ValueError("CSR arrays have one axis and row_offsets holds rows + 1 entries")
+
+
 def csr_spmm(row_offsets, column_indices, values, dense, out=None, *, state=None):
     """`state`: the call's int32 workspace (``workspace(device)`` by default); calls that may overlap
     on different streams need one each."""
-    device = _require_cuda(row_offsets, column_indices, values, dense)
+    device = _require_cuda(row_offsets, column_indices, values, dense, *(() if out is None else (out,)))
+    _csr_operands(row_offsets, column_indices, values)
+    if dense.dim() != 2:
+        raise ValueError("dense must be a matrix")
+    _expect("dense", dense, torch.float32)
     if out is None:
         out = torch.empty((row_offsets.numel() - 1, dense.shape[1]), dtype=torch.float32, device=device)
+    _expect("out", out, torch.float32, (row_offsets.numel() - 1, dense.shape[1]))
+    if state is not None:
+        _expect("state", state, torch.int32)
     _call("b200_csr_spmm", device, *_slots(row_offsets), *_slots(column_indices), *_slots(values),
           *_slots(dense), *_slots(out), *_slots(workspace(device) if state is None else state), _stream(dense))
     return out
 
 
 def csr_spmv(row_offsets, column_indices, values, vector, out=None):
-    device = _require_cuda(row_offsets, column_indices, values, vector)
+    device = _require_cuda(row_offsets, column_indices, values, vector, *(() if out is None else (out,)))
+    _csr_operands(row_offsets, column_indices, values)
+    _expect("vector", vector, torch.float32)
+    if vector.dim() != 1:
+        raise ValueError("vector must have one axis")
     if out is None:
         out = torch.empty((row_offsets.numel() - 1,), dtype=torch.float32, device=device)
+    _expect("out", out, torch.float32, (row_offsets.numel() - 1,))
     _call("b200_csr_spmv", device, *_slots(row_offsets), *_slots(column_indices), *_slots(values),
           *_slots(vector), *_slots(out), _stream(vector))
     return out
 
 
 def softmax_backward(probabilities, upstream, out=None):
-    device = _require_cuda(probabilities, upstream)
+    device = _require_cuda(probabilities, upstream, *(() if out is None else (out,)))
+    _expect("probabilities", probabilities, torch.float32)
+    _expect("upstream", upstream, torch.float32, probabilities.shape)
     if out is None:
         out = torch.empty(probabilities.shape, dtype=probabilities.dtype, device=device)
+    _expect("out", out, torch.float32, probabilities.shape)
     _call("b200_softmax_backward", device, *_slots(probabilities), *_slots(upstream), *_slots(out),
           _CODES[probabilities.dtype], _stream(probabilities))
     return out
@@ -134,17 +195,34 @@ def softmax_backward(probabilities, upstream, out=None):
 
 def layer_norm_backward_rows(x, dy, weight, mean, rstd, dw_partial, db_partial, inverse_features: float, out=None):
     """Returns dx; accumulates into ``dw_partial`` / ``db_partial`` (InOut) in place."""
-    device = _require_cuda(x, dy, weight, mean, rstd, dw_partial, db_partial)
+    device = _require_cuda(x, dy, weight, mean, rstd, dw_partial, db_partial, *(() if out is None else (out,)))
+    _expect("x", x, torch.bfloat16)
+    if x.dim() != 2 or dw_partial.dim() != 2:
+        raise ValueError("layer_norm_backward_rows takes matrices")
+    _expect("dy", dy, torch.bfloat16, x.shape)
+    _expect("weight", weight, torch.bfloat16, (x.shape[1],))
+    _expect("mean", mean, torch.float32, (x.shape[0],))
+    _expect("rstd", rstd, torch.float32, (x.shape[0],))
+    _expect("dw_partial", dw_partial, torch.bfloat16, (dw_partial.shape[0], x.shape[1]))
+    _expect("db_partial", db_partial, torch.bfloat16, dw_partial.shape)
     if out is None:
         out = torch.empty(x.shape, dtype=x.dtype, device=device)
+    _expect("out", out, torch.bfloat16, x.shape)
     _call("b200_layer_norm_backward_rows", device, *_slots(x), *_slots(dy), *_slots(weight), *_slots(mean),
           *_slots(rstd), *_slots(out), *_slots(dw_partial), *_slots(db_partial), float(inverse_features), _stream(x))
     return out
 
 
 def layer_norm_backward_reduce(dw_partial, db_partial, dw=None, db=None):
-    device = _require_cuda(dw_partial, db_partial)
+    device = _require_cuda(dw_partial, db_partial, *(t for t in (dw, db) if t is not None))
+    _expect("dw_partial", dw_partial, torch.bfloat16)
+    if dw_partial.dim() != 2:
+        raise ValueError("the partial sums are matrices")
+    _expect("db_partial", db_partial, torch.bfloat16, dw_partial.shape)
     columns = dw_partial.shape[1]
+    for name, tensor in (("dw", dw), ("db", db)):
+        if tensor is not None:
+            _expect(name, tensor, torch.float32, (columns,))
     if dw is None:
         dw = torch.empty((columns,), dtype=torch.float32, device=device)
     if db is None:
@@ -155,19 +233,38 @@ def layer_norm_backward_reduce(dw_partial, db_partial, dw=None, db=None):
 
 
 def attention_backward_delta(output, grad_output, out=None):
-    device = _require_cuda(output, grad_output)
+    device = _require_cuda(output, grad_output, *(() if out is None else (out,)))
+    _float_type("output", output, (torch.float16, torch.bfloat16))
+    if output.dim() != 4:
+        raise ValueError("attention_backward_delta takes (batch, heads, sequence, head_dim) tensors")
+    _expect("grad_output", grad_output, output.dtype, output.shape)
     if out is None:
         out = torch.empty(output.shape[:3], dtype=torch.float32, device=device)
+    _expect("out", out, torch.float32, output.shape[:3])
     _call("b200_attention_backward_delta", device, *_slots(output), *_slots(grad_output), *_slots(out),
           _CODES[output.dtype], _stream(output))
     return out
 
 
+def _attention_backward_operands(q, k, v, grad_output, lse, delta) -> None:
+    _float_type("q", q, (torch.float16, torch.bfloat16))
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("attention backward takes (batch, heads, sequence, head_dim) tensors")
+    _expect("k", k, q.dtype, (q.shape[0], k.shape[1], k.shape[2], q.shape[3]))
+    _expect("v", v, q.dtype, k.shape)
+    _expect("grad_output", grad_output, q.dtype, q.shape)
+    _expect("lse", lse, torch.float32, q.shape[:3])
+    _expect("delta", delta, torch.float32, q.shape[:3])
+
+
 def attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
                             causal: bool = True, grad_k=None, grad_v=None):
-    device = _require_cuda(q, k, v, grad_output, lse, delta)
+    device = _require_cuda(q, k, v, grad_output, lse, delta, *(t for t in (grad_k, grad_v) if t is not None))
+    _attention_backward_operands(q, k, v, grad_output, lse, delta)
     grad_k = torch.empty(k.shape, dtype=k.dtype, device=device) if grad_k is None else grad_k
     grad_v = torch.empty(v.shape, dtype=v.dtype, device=device) if grad_v is None else grad_v
+    _expect("grad_k", grad_k, q.dtype, k.shape)
+    _expect("grad_v", grad_v, q.dtype, v.shape)
     space = workspace(device)
     _call("b200_attention_backward_dkdv", device, *_slots(q), *_slots(k), *_slots(v), *_slots(grad_output),
           *_slots(lse), *_slots(delta), *_slots(grad_k), *_slots(grad_v), float(scale), *_slots(space),
@@ -177,8 +274,10 @@ def attention_backward_dkdv(q, k, v, grad_output, lse, delta, scale: float, *, h
 
 def attention_backward_dq(q, k, v, grad_output, lse, delta, scale: float, *, head_group: int = 1,
                           causal: bool = True, grad_q=None):
-    device = _require_cuda(q, k, v, grad_output, lse, delta)
+    device = _require_cuda(q, k, v, grad_output, lse, delta, *(() if grad_q is None else (grad_q,)))
+    _attention_backward_operands(q, k, v, grad_output, lse, delta)
     grad_q = torch.empty(q.shape, dtype=q.dtype, device=device) if grad_q is None else grad_q
+    _expect("grad_q", grad_q, q.dtype, q.shape)
     space = workspace(device)
     _call("b200_attention_backward_dq", device, *_slots(q), *_slots(k), *_slots(v), *_slots(grad_output),
           *_slots(lse), *_slots(delta), *_slots(grad_q), float(scale), *_slots(space), _CODES[q.dtype],

@@ -95,3 +95,37 @@ def test_describe_and_doctor_views():
     missing = tools.doctor(None, compiler="/nonexistent/b200-compile")
     assert missing["status"] == "unavailable" and missing["checks"][0]["status"] == "unavailable"
     assert tools.main(["describe"]) == 0
+
+
+def test_direct_operator_calls_validate_before_the_foreign_call(monkeypatch):
+    """`intent_b200.ops` checks element types and extents itself: the kernels trust them, so a
+    wrong index type or a short output buffer must raise here and never reach the library."""
+    from intent_b200 import ops
+
+    def launched(*_):
+        raise AssertionError("the foreign call was reached")
+    monkeypatch.setattr(ops, "_call", launched)
+    monkeypatch.setattr(ops, "_require_cuda", lambda *tensors: tensors[0].device)
+    x = torch.zeros(4, 8)
+    with pytest.raises(TypeError, match="out must have dtype"):
+        ops.softmax(x, out=torch.zeros(4, 8, dtype=torch.float16))
+    with pytest.raises(ValueError, match="out must have shape"):
+        ops.softmax(x, out=torch.zeros(4, 4))
+    with pytest.raises(TypeError, match="weight must have dtype"):
+        ops.layer_norm(x.half(), torch.ones(8), torch.ones(8).half(), 1 / 8, 1e-5)
+    with pytest.raises(TypeError, match="b must have dtype"):
+        ops.gemm(torch.zeros(4, 8, dtype=torch.float16), torch.zeros(8, 4, dtype=torch.bfloat16))
+    with pytest.raises(TypeError, match="a must be one of"):
+        ops.gemm(torch.zeros(4, 8), torch.zeros(8, 4))
+    offsets, columns, values = torch.tensor([0, 1, 2]), torch.tensor([0, 1]), torch.ones(2)
+    with pytest.raises(TypeError, match="row_offsets must have dtype torch.int32"):
+        ops.csr_spmm(offsets, columns.int(), values, torch.zeros(2, 4))       # torch's default int64
+    with pytest.raises(TypeError, match="column_indices must have dtype torch.int32"):
+        ops.csr_spmv(offsets.int(), columns, values, torch.zeros(2))
+    with pytest.raises(ValueError, match="out must have shape"):
+        ops.csr_spmm(offsets.int(), columns.int(), values, torch.zeros(2, 4), out=torch.zeros(3, 4))
+    q = torch.zeros(1, 2, 8, 64, dtype=torch.bfloat16)
+    with pytest.raises(TypeError, match="k must have dtype"):
+        ops.flash_attention(q, q.half(), q, 0.1)
+    with pytest.raises(ValueError, match="out must have shape"):
+        ops.flash_attention(q, q, q, 0.1, out=torch.zeros(1, 2, 8, 32, dtype=torch.bfloat16))
