@@ -80,13 +80,43 @@ def build_library(*, force: bool = False, verbose: bool = False, resource_usage:
     return LIBRARY
 
 
+STRUCTURES = PACKAGE / "compiler" / "structures.inc"
+
+
 def build_compiler(*, force: bool = False) -> Path:
     source = PACKAGE / "compiler" / "b200_compile.cpp"
     COMPILER.parent.mkdir(parents=True, exist_ok=True)
-    if force or _stale(COMPILER, [source]):
+    if force or _stale(COMPILER, [source, STRUCTURES]):
         _run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", "-Wextra", "-o",
               str(COMPILER), str(source)])
     return COMPILER
+
+
+def structure_table() -> str:
+    """The table the compile step checks programs against: family and canonical-structure hash
+    of every packaged kernel IR (``intent_b200/kir/*.mlir``), as ``b200-compile --structure``
+    reports them.  Kernels the provider refuses (the f32 GEMM fixture) are left out."""
+    lines = []
+    for path in sorted((PACKAGE / "kir").glob("*.mlir")):
+        completed = subprocess.run([str(COMPILER), "--structure", "-"], input=path.read_text(encoding="utf-8"),
+                                   capture_output=True, text=True)
+        if completed.returncode:
+            continue
+        family, digest = completed.stdout.split()
+        lines.append(f'    {{"{family}", 0x{digest}ull, "{path.name}"}},\n')
+    return "".join(lines)
+
+
+def refresh_structures() -> bool:
+    """Regenerates structures.inc after the packaged kernel IR changed; returns True when the
+    file changed (the compile step is rebuilt with the new table)."""
+    build_compiler()
+    table = structure_table()
+    if STRUCTURES.exists() and STRUCTURES.read_text() == table:
+        return False
+    STRUCTURES.write_text(table)
+    build_compiler(force=True)
+    return True
 
 
 REFERENCE_INSTALL = ROOT / "baseline" / "_ref"
@@ -132,6 +162,8 @@ if __name__ == "__main__":
     arguments = set(sys.argv[1:])
     if "--resource-usage" in arguments:
         build_library(force=True, resource_usage=True)
+    elif "--structures" in arguments:
+        print("structures.inc", "updated" if refresh_structures() else "is current")
     else:
         build_all(force="--force" in arguments, verbose=True)
     print(LIBRARY)

@@ -287,6 +287,165 @@ long long integer_constant(const std::vector<Operation> &operations, const std::
   fail(kProviderPipeline, "expected " + ssa + " to be an integer constant");
 }
 
+// ---------------------------------------------------------------- structure
+// The census below shortlists a family from operation counts; counts alone would also accept
+// programs that merely look alike (a maximum with a non-zero constant where ReLU has zero,
+// swapped operands of a subtract or divide, dy * (p - sum) for p * (dy - sum)).  So the whole
+// operation graph is compared as well: the IR text is reduced to a canonical form that keeps
+// every operation, attribute, constant, type and operand order but drops what an author may
+// change without changing the computation (source locations, function, parameter and value
+// names, static extents, the HEAD_GROUP divisor), and its hash must be one of the structures
+// this provider has a kernel for (structures.inc, generated from the packaged kernel IR).
+std::string strip_locations(const std::string &ir) {
+  std::string out;
+  out.reserve(ir.size());
+  for (size_t i = 0; i < ir.size();) {
+    if (ir.compare(i, 4, "loc(") == 0 && (i == 0 || !(isalnum((unsigned char)ir[i - 1]) || ir[i - 1] == '_'))) {
+      int depth = 0;
+      bool in_string = false;
+      size_t j = i + 3;
+      for (; j < ir.size(); ++j) {
+        const char c = ir[j];
+        if (in_string) { if (c == '\\') ++j; else if (c == '"') in_string = false; continue; }
+        if (c == '"') in_string = true;
+        else if (c == '(') ++depth;
+        else if (c == ')' && --depth == 0) { ++j; break; }
+      }
+      i = j;
+      continue;
+    }
+    out.push_back(ir[i++]);
+  }
+  return out;
+}
+
+std::string canonical_structure(const std::string &ir, const std::vector<Operation> &operations) {
+  std::string text = strip_locations(ir);
+  // the HEAD_GROUP divisor: the integer constant that is the second operand of floor_divide
+  std::string divisor;
+  for (const Operation &op : operations)
+    if (op.name == "binary" && op.kind == "floor_divide" && op.operands.size() == 2) divisor = op.operands[1];
+  auto erase_quoted_attribute = [&](const std::string &key) {
+    for (size_t at = text.find(key); at != std::string::npos; at = text.find(key, at)) {
+      size_t open = text.find('"', at + key.size());
+      size_t close = open == std::string::npos ? open : text.find('"', open + 1);
+      if (close == std::string::npos) break;
+      text.erase(at, close + 1 - at);
+    }
+  };
+  erase_quoted_attribute("intent.source_module = ");
+  erase_quoted_attribute("intent.source = ");
+  // local variable names the author chose: intent.result_names = ["start", ...]
+  for (size_t at = text.find("intent.result_names = ["); at != std::string::npos;
+       at = text.find("intent.result_names = [", at + 1)) {
+    size_t open = at + strlen("intent.result_names = ");
+    size_t close = text.find(']', open);
+    if (close == std::string::npos) break;
+    text.erase(open + 1, close - open - 1);
+  }
+  // static extents of the views; an integer constant equal to one of them is a loop bound or a
+  // shape of the same instance and is reduced to "E" with them
+  std::vector<std::string> extents;
+  for (size_t at = text.find("tensor<"); at != std::string::npos; at = text.find("tensor<", at + 1)) {
+    size_t j = at + 7;
+    while (j < text.size()) {
+      size_t k = j;
+      while (k < text.size() && isdigit((unsigned char)text[k])) ++k;
+      if (k > j && k < text.size() && text[k] == 'x') { extents.push_back(text.substr(j, k - j)); j = k + 1; }
+      else if (text[j] == '?' && j + 1 < text.size() && text[j + 1] == 'x') j += 2;
+      else break;
+    }
+  }
+  auto is_extent = [&](const std::string &digits) {
+    if (digits == "0" || digits == "1") return false;
+    for (const std::string &extent : extents)
+      if (extent == digits) return true;
+    return false;
+  };
+  std::string out;
+  std::map<std::string, int> names;
+  for (size_t i = 0; i < text.size();) {
+    const char c = text[i];
+    if (c == '%') {                                         // value names, numbered by first appearance
+      size_t j = i + 1;
+      while (j < text.size() && (isalnum((unsigned char)text[j]) || text[j] == '_')) ++j;
+      const std::string name = text.substr(i, j - i);
+      auto found = names.emplace(name, (int)names.size());
+      out += "%" + std::to_string(found.first->second);
+      if (!divisor.empty() && name == divisor && text.compare(j, 21, " = \"intent.constant\"(") == 0) {
+        size_t value = text.find("value = ", j);            // this line defines the divisor
+        size_t line_end = text.find('\n', j);
+        if (value != std::string::npos && value < line_end) {
+          size_t digits = value + 8;
+          while (digits < text.size() && isdigit((unsigned char)text[digits])) ++digits;
+          out += text.substr(j, value + 8 - j) + "G";
+          j = digits;
+        }
+      }
+      i = j;
+    } else if (text.compare(i, 11, "func.func @") == 0) {   // function name
+      size_t j = i + 11;
+      while (j < text.size() && text[j] != '(') ++j;
+      out += "func.func @f";
+      i = j;
+    } else if (text.compare(i, 18, "#intent.parameter<") == 0) {   // parameter name, position kept
+      size_t close = text.find('>', i);
+      size_t comma = text.rfind(',', close);
+      out += "#intent.parameter<" + trim(text.substr(comma + 1, close - comma - 1)) + ">";
+      i = close + 1;
+    } else if (text.compare(i, 7, "tensor<") == 0) {        // static extents -> N, dynamic stay ?
+      size_t j = i + 7;
+      out += "tensor<";
+      while (j < text.size()) {
+        size_t k = j;
+        while (k < text.size() && isdigit((unsigned char)text[k])) ++k;
+        if (k > j && k < text.size() && text[k] == 'x') { out += "Nx"; j = k + 1; }
+        else if (text[j] == '?' && j + 1 < text.size() && text[j + 1] == 'x') { out += "?x"; j += 2; }
+        else break;
+      }
+      i = j;
+    } else if (text.compare(i, 8, "value = ") == 0 && i + 8 < text.size() && isdigit((unsigned char)text[i + 8])) {
+      size_t j = i + 8;
+      while (j < text.size() && isdigit((unsigned char)text[j])) ++j;
+      const std::string digits = text.substr(i + 8, j - i - 8);
+      out += (text.compare(j, 6, " : i64") == 0 && is_extent(digits)) ? std::string("value = E") : "value = " + digits;
+      i = j;
+    } else if (isspace((unsigned char)c)) {                 // runs of white space -> one blank
+      if (!out.empty() && out.back() != ' ') out.push_back(' ');
+      ++i;
+    } else {
+      out.push_back(c);
+      ++i;
+    }
+  }
+  return out;
+}
+
+unsigned long long structure_hash(const std::string &canonical) {
+  unsigned long long hash = 1469598103934665603ull;         // FNV-1a
+  for (unsigned char c : canonical) { hash ^= c; hash *= 1099511628211ull; }
+  return hash;
+}
+
+struct KnownStructure {
+  const char *family;
+  unsigned long long hash;
+  const char *origin;
+};
+const KnownStructure kKnownStructures[] = {
+#include "structures.inc"
+    {nullptr, 0, nullptr}};
+
+void require_known_structure(const std::string &family, unsigned long long hash) {
+  for (const KnownStructure *known = kKnownStructures; known->family; ++known)
+    if (family == known->family && hash == known->hash) return;
+  std::ostringstream message;
+  message << "b200 has no kernel for this program: its operation counts are those of the " << family
+          << " family, but its operations, constants or operand order differ from every " << family
+          << " kernel this provider implements (structure " << std::hex << hash << ")";
+  fail(kProviderPipeline, message.str());
+}
+
 // ---------------------------------------------------------------- the plan
 struct TailConstant {
   std::string name;
@@ -687,13 +846,14 @@ bool parse_bool(const std::string &text, bool *value) {
 int main(int argc, char **argv) {
   std::string target, target_options, input_stage = "kir", ir_output, source_output, metadata_output, input = "-", value;
   CompileOptions options;
-  bool info = false, stop_kir = false, stop_shared = false, any_other = false;
+  bool info = false, stop_kir = false, stop_shared = false, any_other = false, structure_only = false;
   for (int i = 1; i < argc; ++i) {
     const std::string argument = argv[i];
     bool flag = false;
     if (argument == "--compiler-info") { info = true; continue; }
     any_other = true;
-    if (argument == "--stop-after-kir") stop_kir = true;
+    if (argument == "--structure") structure_only = true;     // print "<family> <hash>" of the program on stdin
+    else if (argument == "--stop-after-kir") stop_kir = true;
     else if (argument == "--stop-after-shared") stop_shared = true;
     else if (option_value(argument, "target", &target)) {}
     else if (option_value(argument, "target-options", &target_options)) {}
@@ -731,6 +891,7 @@ int main(int argc, char **argv) {
                  "\"optimization_remarks\": false}, \"failure_stages\": " << kFailureStages << "}\n";
     return 0;
   }
+  if (structure_only) { target = "b200"; ir_output = source_output = "-"; }   // nothing is written in this mode
   if (stop_kir && stop_shared) { std::cerr << "--stop-after-kir and --stop-after-shared are mutually exclusive\n"; return kInvocation; }
   if (input_stage != "kir" && input_stage != "shared") { std::cerr << "--input-stage must be kir or shared\n"; return kInvocation; }
   if (!stop_kir && target.empty()) { std::cerr << "--target is required unless --stop-after-kir is selected\n"; return kInvocation; }
@@ -767,6 +928,11 @@ int main(int argc, char **argv) {
     std::string function;
     std::vector<Parameter> parameters = parse_signature(ir, &function);
     std::vector<Operation> operations = parse_operations(ir);
+    if (structure_only) {
+      const Plan plan = classify(parameters, operations);
+      std::cout << plan.family << " " << std::hex << structure_hash(canonical_structure(ir, operations)) << "\n";
+      return 0;
+    }
     if (!provider_stage) {
       if (!write_file(ir_output, ir)) fail(kOutput, "cannot write " + ir_output);
       return 0;
@@ -778,6 +944,7 @@ int main(int argc, char **argv) {
         capabilities.find("\"compute_capability_major\":10") == std::string::npos)
       fail(kProviderPipeline, "b200 holds sm_100a kernels only; the target reports another compute capability");
     const Plan plan = classify(parameters, operations);
+    require_known_structure(plan.family, structure_hash(canonical_structure(ir, operations)));
     if (options.remarks) std::cerr << "remark: " << function << " -> " << plan.family << " (" << plan.entry << ")\n";
     if (!write_file(ir_output, ir)) fail(kOutput, "cannot write " + ir_output);
     if (!write_file(source_output, source_text(function, plan))) fail(kOutput, "cannot write " + source_output);

@@ -127,3 +127,57 @@ def test_generated_program_round_trip(tmp_path):
     assert loaded.metadata == program.metadata and loaded.source == program.source and loaded.ir == program.ir
     with pytest.raises(b200.CompilationStageError):
         program.save(saved)
+
+
+def _refused(text):
+    with pytest.raises(b200.CompilationStageError) as error:
+        compile_text(text)
+    assert error.value.stage == "provider_pipeline"
+    return str(error.value)
+
+
+def test_programs_that_only_look_like_a_family_are_refused():
+    """The operation counts shortlist a family; the operation graph must then be one of the
+    structures the provider implements.  Near misses get the pipeline error, never another kernel."""
+    relu = (KIR / "gemm_relu.mlir").read_text()
+    assert "value = 0x0000000000000000 : f64" in relu
+    # maximum(acc, 1.0) has the counts of the ReLU epilogue, but is not ReLU
+    message = _refused(relu.replace("value = 0x0000000000000000 : f64", "value = 0x3FF0000000000000 : f64"))
+    assert "gemm" in message and "differ" in message
+    softmax = (KIR / "stable_softmax.mlir").read_text()
+    # exp(max - x) instead of exp(x - max): same counts, operands of the subtract swapped
+    assert '"intent.binary"(%v8, %v15)' in softmax
+    _refused(softmax.replace('"intent.binary"(%v8, %v15)', '"intent.binary"(%v15, %v8)'))
+    # d / 1.0 instead of 1.0 / d
+    assert '"intent.binary"(%v23, %v22)' in softmax
+    _refused(softmax.replace('"intent.binary"(%v23, %v22)', '"intent.binary"(%v22, %v23)'))
+    # an approximate exponential is another numerics contract
+    norm = (KIR / "layer_norm_f16.mlir").read_text()
+    assert "unary_operator<rsqrt>" in norm
+    _refused(norm.replace("unary_operator<rsqrt>", "unary_operator<sqrt>"))
+
+
+def test_what_an_author_may_rename_does_not_change_the_structure():
+    """Function, parameter, value and local names, source locations and static extents are not
+    part of a program's structure: the two CSR instances (8192 and 262144 rows) are one kernel."""
+    import re
+    import subprocess
+    from intent_b200.build import STRUCTURES, structure_table
+
+    def structure(text):
+        done = subprocess.run([str(b200.COMPILER), "--structure", "-"], input=text, capture_output=True, text=True)
+        assert done.returncode == 0, done.stderr
+        return done.stdout.split()
+
+    small, large = (structure((KIR / name).read_text()) for name in ("csr_spmm.mlir", "csr_spmm_262144.mlir"))
+    assert small == large and small[0] == "csr_spmm"
+    text = (KIR / "stable_softmax.mlir").read_text()
+    renamed = re.sub(r'loc\("[^"]*":\d+:\d+\)', 'loc("elsewhere.py":1:1)', text)
+    renamed = renamed.replace("@stable_softmax", "@my_kernel").replace('"x", 0', '"inputs", 0')
+    renamed = re.sub(r"%v(\d+)", lambda m: f"%t{int(m.group(1)) + 100}", renamed)
+    assert structure(renamed) == structure(text)
+    compile_text(renamed)                                          # and it still compiles to the softmax entry
+    attention = (KIR / "flash_attention_bf16_fwd.mlir").read_text()
+    grouped = b200.kernels.flash_attention_bf16_fwd.kir({"HEAD_GROUP": 8, "CAUSAL": True})
+    assert grouped != attention and structure(grouped) == structure(attention)
+    assert STRUCTURES.read_text() == structure_table(), "run `python -m intent_b200.build --structures`"
