@@ -223,8 +223,10 @@ int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a
  * kernel's bounded waits use live in a device array that is part of this
  * library: B200_WORKSPACE_WORDS int32 words (256 bytes), held by every GPU
  * that loads the library until the process exits.  The call itself makes no
- * cudaMalloc / cudaFree and no other allocating library call, and keeps no
- * host-side cache.
+ * cudaMalloc / cudaFree and no other allocating library call.  On the host it
+ * remembers one thing per device for the life of the process: the array's
+ * address (a table of 64 pointers inside the library), so a device that is
+ * reset while the process keeps running is not supported.
  *
  * Arguments are b200_gemm's without the workspace view, plus wait_and_check:
  *   0  enqueue only, like b200_gemm; a device-side timeout goes unreported;
@@ -232,7 +234,9 @@ int b200_gemm(const void *a, int64_t a_d0, int64_t a_d1, int64_t a_s0, int64_t a
  *      bounded wait gave up.
  * Limits: each of M, N, K at most B200_STATIC_SCRATCH_MAX_EXTENT; larger
  * problems are refused with B200_ERR_UNSUPPORTED_LAYOUT.  Layout rules are
- * b200_gemm's.
+ * b200_gemm's except for B, which must be K-major here (b_s0 == 1, the
+ * "column-major (K,N)" layout); b200_gemm's second layout, N-major B, is
+ * refused with B200_ERR_UNSUPPORTED_LAYOUT.
  * The first call on a device looks the array's address up (one
  * cudaGetSymbolAddress with that device current); make that call before any
  * stream capture begins.  All calls on one GPU share the array: every call
@@ -331,6 +335,16 @@ int b200_csr_validate(const void *row_offsets, int64_t rows, const void *column_
  */
 int b200_gather_probe(const void *table, int64_t table_rows, int64_t gathers, int32_t variant,
                       int32_t hints, void *sink, void *workspace, void *stream);
+
+/*
+ * Runs the bounded-wait path of the tensor-core kernels on purpose: one CTA waits, with a limit
+ * of `limit_cycles` (1e3..2e8), for an mbarrier that nothing arrives on.  The wait gives up,
+ * words 0-1 of the workspace become {1, site 9}, words 8-9 record {0 = "did not arrive", 1 =
+ * "another warp saw the abort flag"}, and the kernel returns; b200_workspace_status then
+ * reports B200_ERR_DEVICE_TIMEOUT.  Nothing faults or hangs.  For tests of the failure
+ * reporting; no counterpart in the reference, which has no device-side waits of its own.
+ */
+int b200_selftest_bounded_wait(void *workspace, int64_t ws_d0, int64_t ws_s0, int64_t limit_cycles, void *stream);
 
 /*
  * Reads word 0 of a workspace after synchronising `stream`: B200_OK, or

@@ -8,10 +8,14 @@ reference's rule that a failing backend never switches provider
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 from threading import Lock
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / "libintent_b200.so"
+# INTENT_B200_CHECKED=1 selects the build with device-side index checks (python -m intent_b200.build
+# compiles both); it is slower and meant for debugging a caller's CSR arrays, not for production.
+_CHECKED = os.environ.get("INTENT_B200_CHECKED", "") not in ("", "0")
+LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / ("libintent_b200_checked.so" if _CHECKED else "libintent_b200.so")
 
 OK = 0
 ERR_INVALID_ARGUMENT = 1
@@ -48,6 +52,7 @@ SIGNATURES = {
     "b200_csr_validate": [_P, _I64, _P, _I64, _I64, ctypes.POINTER(_I64), _P],
     "b200_gather_probe": [_P, _I64, _I64, _I32, _I32, _P, _P, _P],
     "b200_workspace_status": [_P, ctypes.POINTER(_I32), _P],
+    "b200_selftest_bounded_wait": _view(1) + [_I64, _P],
     "b200_device_check": [ctypes.c_int],
     "b200_device_capabilities": [ctypes.c_int, ctypes.POINTER(_I64)],
     "b200_abi_version": [],

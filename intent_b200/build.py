@@ -52,18 +52,26 @@ def _run(command: list[str]) -> str:
     return completed.stdout + completed.stderr
 
 
-def build_library(*, force: bool = False, verbose: bool = False, resource_usage: bool = False) -> Path:
+CHECKED_LIBRARY = PACKAGE / "lib" / "libintent_b200_checked.so"
+
+
+def build_library(*, force: bool = False, verbose: bool = False, resource_usage: bool = False,
+                  checked: bool = False) -> Path:
+    """``checked=True`` builds the variant with device-side index checks (-DB200_CHECKED) as
+    ``libintent_b200_checked.so``; ``INTENT_B200_CHECKED=1`` makes the package load it."""
     sources = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.cuh")) + [ROOT / "include" / "intent_b200.h"]
-    OBJECTS.mkdir(parents=True, exist_ok=True)
-    LIBRARY.parent.mkdir(parents=True, exist_ok=True)
+    objects_directory = ROOT / "build" / "obj_checked" if checked else OBJECTS
+    library = CHECKED_LIBRARY if checked else LIBRARY
+    objects_directory.mkdir(parents=True, exist_ok=True)
+    library.parent.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(source: Path) -> tuple[Path, str]:
-        target = OBJECTS / (source.stem + ".o")
+        target = objects_directory / (source.stem + ".o")
         log = ""
         if force or resource_usage or _stale(target, [source, *headers]):
-            flags = NVCC_FLAGS + (["-Xptxas", "-v"] if resource_usage else [])
+            flags = NVCC_FLAGS + (["-Xptxas", "-v"] if resource_usage else []) + (["-DB200_CHECKED"] if checked else [])
             log = _run([nvcc, *flags, "-c", str(source), "-o", str(target)])
         return target, log
 
@@ -74,10 +82,10 @@ def build_library(*, force: bool = False, verbose: bool = False, resource_usage:
         for _, log in results:
             if log.strip():
                 print(log)
-    if force or _stale(LIBRARY, objects):
-        _run([nvcc, "-shared", "-o", str(LIBRARY), *map(str, objects), "-gencode",
+    if force or _stale(library, objects):
+        _run([nvcc, "-shared", "-o", str(library), *map(str, objects), "-gencode",
               "arch=compute_100a,code=sm_100a"])
-    return LIBRARY
+    return library
 
 
 STRUCTURES = PACKAGE / "compiler" / "structures.inc"
@@ -154,6 +162,7 @@ def install_reference() -> Path | None:
 
 def build_all(*, force: bool = False, verbose: bool = False) -> None:
     build_library(force=force, verbose=verbose)
+    build_library(force=force, verbose=verbose, checked=True)
     build_compiler(force=force)
     install_reference()
 

@@ -97,6 +97,8 @@ extern "C" int b200_workspace_status(const void *workspace, int32_t *detail, voi
   B200_CUDA_TRY(cudaMemcpyAsync(words, workspace, sizeof words, cudaMemcpyDeviceToHost, s));
   B200_CUDA_TRY(cudaStreamSynchronize(s));
   if (detail) *detail = words[1];
+  if (words[0] == 2)   // only the checked build (-DB200_CHECKED) writes this
+    return fail(B200_ERR_INVALID_ARGUMENT, "checked build: an index or offset was outside its array (row %d)", words[1]);
   if (words[0] != 0)
     return fail(B200_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (site %d)", words[1]);
   return B200_OK;

@@ -74,8 +74,9 @@ csr_spmm_scalar_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
 // caller) that carries "every row seen so far ascends" from the first launch of a call, which
 // sets it and clears it on meeting a descending row, to the later launches of the same call.
 // Nothing of a call lives in library-global device memory, so calls on different streams
-// cannot see one another's flag.  (Words 0 and 1 are the timeout report of the tensor-core
-// entries; this operator has no bounded wait and never writes them.)
+// cannot see one another's flag.  (Words 0 and 1 are the status report b200_workspace_status
+// reads: this operator has no bounded wait and writes them only in the checked build, as
+// {2, row} when it met an offset or a column outside its array.)
 constexpr int kStateSorted = 2;
 
 __global__ void spmm_begin_kernel(int *state) { state[kStateSorted] = 1; }
@@ -149,7 +150,8 @@ __global__ void __launch_bounds__(kRowsWarps * 32, kRowsCtas)
 csr_spmm_rows_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ column_indices,
                      const float *__restrict__ values, const float *__restrict__ dense,
                      float *__restrict__ output, int rows, int features, uint32_t dense_pitch16,
-                     uint32_t output_pitch16, int column_lo, int column_hi, int phase, int *state) {
+                     uint32_t output_pitch16, int column_lo, int column_hi, int phase, int *state, int columns,
+                     int stored_elements) {
   struct __align__(8) Term { uint32_t offset; float value; };   // offset of the X row in 16-byte units
   __shared__ Term terms[kRowsWarps][32];
   // ACCUMULATE is false only for launch 0, which never reads partial sums; a later launch decides here
@@ -173,8 +175,13 @@ csr_spmm_rows_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__r
   const unsigned below = (1u << lane) - 1u;
   Term *mine_terms = terms[warp];
 
+#ifdef B200_CHECKED
+  auto index_of = [&](int at) { return at >= 0 && at < stored_elements ? __ldcs(column_indices + at) : -1; };
+  auto value_of = [&](int at) { return at >= 0 && at < stored_elements ? __ldcs(values + at) : 0.0f; };
+#else
   auto index_of = [&](int at) { return __ldcs(column_indices + at); };
   auto value_of = [&](int at) { return __ldcs(values + at); };
+#endif
   auto partial_of = [&](int r) { return __ldcs(result + (uint64_t)r * output_pitch16); };
   const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 
@@ -213,7 +220,15 @@ csr_spmm_rows_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__r
         column = 0; value = 0.0f;
         if (base + lane < stop) { column = index_of(base + lane); value = value_of(base + lane); }
       }
-      const bool stored = base + lane < stop;
+      bool stored = base + lane < stop;
+#ifdef B200_CHECKED
+      // Checked build: the kernel trusts the CSR arrays (the definition's assume_in_bounds); here an
+      // offset or a column outside its array is recorded in the workspace ({2, row}) and the term is
+      // dropped instead of being loaded, so a corrupted matrix ends as an error status, not a fault.
+      const bool bad = stored && (base + lane >= stored_elements || column < 0 || column >= columns);
+      if (__any_sync(0xffffffffu, bad || stop < start) && lane == 0 && atomicCAS(&state[0], 0, 2) == 0) state[1] = row;
+      stored = stored && !bad && stop >= start;
+#endif
       if (check_order) {
         const int before = __shfl_up_sync(0xffffffffu, column, 1);
         const bool descends = stored && column < (lane == 0 ? previous : before);
@@ -460,7 +475,8 @@ extern "C" int b200_csr_spmm(const void *row_offsets, int64_t ro_d0, int64_t ro_
       const dim3 grid((unsigned)(wanted < resident ? wanted : resident), chunks);
       kernel<<<grid, kRowsWarps * 32, 0, s>>>((const int32_t *)row_offsets, (const int32_t *)column_indices,
                                                (const float *)values, (const float *)dense, (float *)output, (int)rows,
-                                               (int)x_d1, (uint32_t)(x_s0 / 4), (uint32_t)(y_s0 / 4), lo, hi, phase, state);
+                                               (int)x_d1, (uint32_t)(x_s0 / 4), (uint32_t)(y_s0 / 4), lo, hi, phase, state,
+                                               (int)(x_d0 > INT32_MAX ? INT32_MAX : x_d0), (int)ci_d0);
     };
     if (phase == 0) launch(csr_spmm_rows_kernel<false>);
     else launch(csr_spmm_rows_kernel<true>);

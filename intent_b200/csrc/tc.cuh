@@ -22,6 +22,7 @@ enum WaitSite : int {
   kSiteCorrection = 6,
   kSiteDrain = 7,
   kSiteOther = 8,
+  kSiteSelfTest = 9,
 };
 
 // About two seconds at 2 GHz; a wait that long means a lost arrival.
@@ -71,14 +72,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // aborted (`*abort_flag` non-zero, a shared-memory word); the first role to give
 // up publishes the site in the workspace so the host can report it.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int site) {
+                                          int *status, int site, long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - start > kWaitCycles) {
+      if (clock64() - start > limit) {
         *abort_flag = 1;
         if (atomicCAS(status, 0, 1) == 0) status[1] = site;
         __threadfence();

@@ -30,6 +30,15 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(handle, name), f"{name} is declared but not exported"
 
 
+def test_checked_build_exports_the_same_symbols():
+    """The variant with device-side index checks (-DB200_CHECKED) is built beside the regular
+    library and is a drop-in for it."""
+    from intent_b200 import build
+    handle = ctypes.CDLL(str(build.CHECKED_LIBRARY))
+    for name in declared_functions():
+        assert hasattr(handle, name), f"{name} is missing from the checked build"
+
+
 def test_python_signatures_match_header_arity():
     declared = declared_functions()
     for name, argtypes in _native.SIGNATURES.items():

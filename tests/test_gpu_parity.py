@@ -425,3 +425,75 @@ def test_csr_spmm_calls_on_two_streams_do_not_share_state(monkeypatch):
             outs[0].zero_()
             outs[1].zero_()
     assert int(states[0][2]) == 1 and int(states[1][2]) == 0      # word 2: "every row ascends"
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_workspace_recovers():
+    """Failure detection without a fault: a wait on a barrier that nothing arrives on gives up
+    after a short limit, the kernel returns, the host reads B200_ERR_DEVICE_TIMEOUT with the site
+    of the wait, and after clearing the words the same workspace serves an ordinary call."""
+    import ctypes
+    from intent_b200 import _native
+    space = torch.zeros(64, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    with torch.cuda.device(DEV):
+        status = _native.entry("b200_selftest_bounded_wait")(space.data_ptr(), 64, 1, 2_000_000, stream)
+        assert status == _native.OK
+        detail = ctypes.c_int32(0)
+        status = _native.entry("b200_workspace_status")(space.data_ptr(), ctypes.byref(detail), stream)
+    assert status == _native.ERR_DEVICE_TIMEOUT and detail.value == 9          # site of the self-test wait
+    with pytest.raises(_native.NativeCallError, match="bounded device-side wait gave up"):
+        _native.check("b200_workspace_status", status)
+    words = space.cpu()
+    assert words[0] == 1 and words[8] == 0 and words[9] == 1     # did not arrive; the other warp saw the abort flag
+    space.zero_()
+    a, b = workloads.gemm_inputs(256, 256, 128, seed=77)
+    c = torch.empty(256, 256, dtype=torch.float16, device=DEV)
+    bd = b.t().contiguous().to(DEV).t()
+    ad = a.to(DEV)
+    with torch.cuda.device(DEV):
+        status = _native.entry("b200_gemm")(ad.data_ptr(), *ad.shape, *ad.stride(), bd.data_ptr(), *bd.shape, *bd.stride(),
+                                            c.data_ptr(), *c.shape, *c.stride(), space.data_ptr(), 64, 1, 1, 0, stream)
+        assert status == _native.OK
+        assert _native.entry("b200_workspace_status")(space.data_ptr(), ctypes.byref(detail), stream) == _native.OK
+    assert relative_error(c, oracle.gemm(a, b)) <= 1e-2
+    with pytest.raises(ValueError):
+        _native.check("b200_selftest_bounded_wait",
+                      _native.entry("b200_selftest_bounded_wait")(space.data_ptr(), 64, 1, 10, stream))   # limit too small
+
+
+CHECKED_SCRIPT = """
+import sys, torch
+sys.path.insert(0, %r)
+import oracle
+from intent_b200 import _native, ops, workloads
+assert _native.LIBRARY_PATH.name == "libintent_b200_checked.so"
+ro, ci, va, x = workloads.csr_inputs(4096, 4096, 32, 128, seed=9)
+d = [t.to("cuda:0") for t in (ro, ci, va, x)]
+assert torch.equal(ops.csr_spmm(*d).cpu(), oracle.csr_spmm(ro, ci, va, x)), "the checked build computes the same product"
+ops.workspace_status("cuda:0")
+bad = ci.clone()
+bad[32 * 1000 + 5] = 4096            # one column past the last row of X, in row 1000
+y = ops.csr_spmm(d[0], bad.to("cuda:0"), d[2], d[3])
+try:
+    ops.workspace_status("cuda:0")
+    print("not reported")
+except ValueError as error:
+    assert "row 1000" in str(error), str(error)
+    print("reported")
+expected = oracle.csr_spmm(ro, ci, va, x)
+assert torch.equal(y.cpu()[:1000], expected[:1000]) and torch.equal(y.cpu()[1001:], expected[1001:])
+"""
+
+
+def test_checked_build_reports_an_out_of_range_column_instead_of_loading_it():
+    """The -DB200_CHECKED variant of the library (INTENT_B200_CHECKED=1): an index outside X is
+    recorded in the workspace with its row and the term is skipped, so nothing is read out of
+    bounds; every other row is unaffected."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parents[1])
+    done = subprocess.run([sys.executable, "-c", CHECKED_SCRIPT % root], env=dict(os.environ, INTENT_B200_CHECKED="1"),
+                          capture_output=True, text=True)
+    assert done.returncode == 0 and "reported" in done.stdout and "not reported" not in done.stdout, done.stderr[-2000:]
