@@ -257,6 +257,7 @@ class EndToEnd:
         b200, device = case.b200, case.device
         kernel = case.kernel(world, False)
         self.slots = []
+        self.pinned = {}
         self.h2d = self.d2h = 0
         for _ in range(2):
             scope = b200.HostBuffers(device)
@@ -266,8 +267,9 @@ class EndToEnd:
                     operands.append(value)
                 elif position in case.resident:
                     operands.append(value.to(device))
-                else:
-                    operands.append(scope.input(value, region=case.input_region(position, world)))
+                else:    # the step's inputs travel from page-locked host memory
+                    pinned = self.pinned.setdefault(position, b200.HostBuffers.page_locked(value))
+                    operands.append(scope.input(pinned, region=case.input_region(position, world)))
             call = kernel.prepare(*operands)
             results = call.result() if isinstance(call.result(), tuple) else (call.result(),)
             for result in results:
@@ -588,7 +590,8 @@ class SequenceEndToEnd(EndToEnd):
         self.slots = []
         for _ in range(2):
             scope = b200.HostBuffers(device)
-            calls, results = case.build([scope.input(t) for t in case.host])
+            self.pinned = getattr(self, "pinned", None) or [b200.HostBuffers.page_locked(t) for t in case.host]
+            calls, results = case.build([scope.input(t) for t in self.pinned])
             for result in results:
                 scope.result(result)
             sequence = b200.PreparedSequence(calls, outputs=tuple(results), owners=(scope,))

