@@ -1053,12 +1053,13 @@ def main() -> None:
     measured = {name: row["frac"] for name, row in per_op.items() if "frac" in row and name in BASELINE_OPS}
     roofline = dict(head["roofline"])
     roofline["per_op"] = per_op
+    roofline["per_op_note"] = ("the metric is per operator: this line's value is the LayerNorm configuration, per_op holds "
+                               "every configuration measured in this run, min_frac the lowest roofline fraction of the five")
     if measured:
         roofline["min_frac_op"] = min(measured, key=measured.get)
         roofline["min_frac"] = measured[roofline["min_frac_op"]]
     line = {
-        "metric": f"{head['op']} throughput (algorithmic {'bytes' if head['unit'] == 'GB/s' else 'flops'} / time); "
-                  "the other configurations of the per-operator metric are under roofline.per_op",
+        "metric": f"{head['op']} throughput (algorithmic {'bytes' if head['unit'] == 'GB/s' else 'flops'} / time)",
         "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": arguments.steps,
         "warmup": arguments.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,

@@ -66,6 +66,25 @@ def _rank(rank: int, world: int, port: int, failures):
             ro.to(device), ci.to(device), va.to(device), dense.to(device))
         assert torch.equal(y.cpu(), oracle.csr_spmm(ro, ci, va, dense)), "csr_spmm is not bit-exact"
 
+        # the same options through the reference's own front door (its option gate and target resolution)
+        from conftest import HAS_REFERENCE, REFERENCE_PYTHON
+        if HAS_REFERENCE:
+            import sys
+            import tempfile
+            sys.path.insert(0, str(REFERENCE_PYTHON))
+            os.environ["INTENT_CACHE_DIR"] = tempfile.mkdtemp(prefix=f"intent-cache-{rank}-")
+            os.environ.pop("INTENT_COMPILER", None)
+            import intent
+            b200.register()
+            from intent.examples.kernels.normalization.layer_norm import layer_norm_f16
+            x, w, b, inv, eps = workloads.layer_norm_inputs(130, 2048, seed=27)
+            kernel = intent.jit(layer_norm_f16, backend="b200", backend_options=options)
+            y = kernel.run(x.to(device), w.to(device), b.to(device), inv, eps)
+            assert relative_error(y, oracle.layer_norm(x, w, b, inv, eps)) <= 1e-2, "layer_norm through intent.jit"
+            with pytest.raises(ValueError, match="unsupported local b200 options"):
+                intent.jit(layer_norm_f16, backend="b200", backend_options={"ranks": 2}).prepare(
+                    x.to(device), w.to(device), b.to(device), inv, eps)
+
         # without gather_output only the rank's own block is written
         (x,) = workloads.softmax_inputs(64, 512, seed=26)
         out = torch.full((64, 512), -1.0, device=device)
