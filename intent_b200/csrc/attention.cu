@@ -14,13 +14,18 @@
 //                halves, 128-byte swizzle)
 //   warp 1       MMA issuer:  S = Q . K_j^T   (A, B from shared memory, K-major)
 //                             O += P . V_j    (A = P from TMEM, B = V MN-major),
-//                issued as two halves of 64 keys, each as soon as its P is ready
+//                issued as two halves of 64 keys, each as soon as its P is ready.
+//                The whole warp walks the loop (waits and descriptor arithmetic
+//                stay warp-uniform, descriptors are built once and advanced by
+//                adding byte offsets / 16); one elected lane issues a product per
+//                branch.
 //   warps 2..9   softmax of tile A, warps 10..17 softmax of tile B.  Two threads
 //                share a query row: thread (row, h) owns the score columns
-//                [32h, 32h+32) and [64+32h, 64+32h+32).  Pass 1 reads them from
-//                TMEM (tcgen05.ld) for the row maximum, which the two threads
-//                exchange through shared memory; pass 2 reads them again, 32 at a
-//                time, p = ex2.approx.ftz(s*scale*log2e - m), f32 partial row sum,
+//                [32h, 32h+32) and [64+32h, 64+32h+32), handled 16 at a time with
+//                the TMEM read (tcgen05.ld) of the next 16 in flight.  Pass 1
+//                takes the row maximum, which the two threads exchange through
+//                shared memory; pass 2 reads the scores again,
+//                p = ex2.approx.ftz(s*scale*log2e - m), f32 partial row sum,
 //                P rounded to the operand type and written over the first 16 of
 //                the 32 score columns it came from (tcgen05.st), then the half's
 //                barrier is signalled.  The running maximum is only replaced, and
@@ -28,6 +33,13 @@
 //                accumulator stays exact in the usual online-softmax sense while
 //                rescales stay rare.  Last: the two partial sums are added and
 //                each thread writes its half of O * div.approx.ftz(1, sum).
+//
+// Measured timeline of one step (both tiles, 128 keys) at the heaviest CTA: about
+// 3200 clocks, of which the tensor pipe is busy 2048; per tile the chain is
+// softmax (about 2000: 480 to the maximum, 1500 for the exponentials at 12 clocks
+// per 32 of them and sub-partition) -> P.V second half + S (768) -> hand-offs (380).
+// Under sustained load the part runs at its power cap (about 1.7 GHz), so the step
+// time in seconds follows the clock.
 //
 // TMEM (512 columns): S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512).
 // Causal tiles that lie entirely above the diagonal are never visited (tile A
@@ -45,7 +57,8 @@ namespace {
 constexpr int kBlockM = 128;                     // query rows per tile (two tiles per CTA)
 constexpr int kBlockN = 128;
 constexpr int kMaxHeadDim = 128;                 // head dimension is a template parameter: 64 or 128
-constexpr int kThreads = 576;                    // producer warp, MMA warp, 2 tiles x 2 column halves x 4 warps
+constexpr int kFirstSoftmaxWarp = 2;             // warp 0: TMA producer, warp 1: MMA issuer
+constexpr int kThreads = (kFirstSoftmaxWarp + 16) * 32;     // + 2 tiles x 2 column halves x 4 warps
 constexpr int kTmemColumns = 512;
 constexpr int kRingSlots = 4;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // shared-memory slot of one Q / K / V tile (half used at head dim 64)
@@ -139,7 +152,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     for (int x = 0; x < 2; ++x) {
       tc::mbar_init(&bars->s_full[x], 1);
-      tc::mbar_init(&bars->p_ready[x][0], 8);
+      tc::mbar_init(&bars->p_ready[x][0], 8);   // one arrival per softmax warp of the tile
       tc::mbar_init(&bars->p_ready[x][1], 8);
       tc::mbar_init(&bars->o_full[x], 1);
     }
@@ -194,83 +207,90 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- MMA issuer
-    if (tc::elect_one()) {
-      constexpr int format = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_s = tc::instr_desc_f16(format, kBlockM, kBlockN, false);
-      constexpr uint32_t idesc_o = tc::instr_desc_f16(format, kBlockM, kHeadDim, true);
-      const uint32_t ring_address = tc::smem_u32(ring);
-      bool alive = tc::mbar_wait(&bars->q_full, 0, abort_flag, status, tc::kSiteMmaFull);
+    // The whole warp walks the loop, so waits, slot and descriptor arithmetic stay warp-uniform; one
+    // elected lane issues the tcgen05 instructions, a whole product per branch.  The issue order
+    //   S_A(j), P.V_B(j-1), S_B(j), P.V_A(j), S_A(j+1), ...
+    // keeps the two tiles in opposite phase: one tile's softmax runs while the other tile's products
+    // occupy the tensor pipe.
+    const bool issuer = tc::elect_one();
+    constexpr int format = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr uint32_t idesc_s = tc::instr_desc_f16(format, kBlockM, kBlockN, false);
+    constexpr uint32_t idesc_o = tc::instr_desc_f16(format, kBlockM, kHeadDim, true);
+    // descriptors of the first 16-element slice; a slice further on adds its byte offset / 16
+    const uint64_t desc_q = tc::smem_desc_k_major_sw128(tc::smem_u32(q_tiles));
+    const uint64_t desc_k = tc::smem_desc_k_major_sw128(tc::smem_u32(ring));
+    const uint64_t desc_v = tc::smem_desc_mn_major_sw128(tc::smem_u32(ring), kHalfBytes);
 
-      // S_x(j) = Q_x . K_j^T into the score columns of tile x
-      auto issue_scores = [&](int x, int j) {
-        const uint32_t q_address = tc::smem_u32(q_tiles + x * kTileBytes);
-        const uint32_t k_address = ring_address + RingPosition(2 * j).slot * kTileBytes;
+    auto wait_slot = [&](int index) {
+      const RingPosition at(index);
+      return tc::mbar_wait(&bars->slot_full[at.slot], at.phase, abort_flag, status, tc::kSiteMmaFull);
+    };
+    auto release_slot = [&](int index) {      // arrives once the products issued so far have read the slot
+      if (issuer) tc::mma_commit(&bars->slot_empty[RingPosition(index).slot]);
+    };
+    // S_x(j) = Q_x . K_j^T into the score columns of tile x
+    auto issue_scores = [&](int x, int j) {
+      const uint64_t desc_qx = desc_q + ((x * kTileBytes) >> 4);
+      const uint64_t desc_kj = desc_k + ((RingPosition(2 * j).slot * kTileBytes) >> 4);
+      if (issuer) {
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-          const uint32_t offset = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-          tc::mma_f16_ss(tmem_base + x * kBlockN, tc::smem_desc_k_major_sw128(q_address + offset),
-                         tc::smem_desc_k_major_sw128(k_address + offset), idesc_s, kk != 0);
+          const uint32_t offset = ((kk / 4) * kHalfBytes + (kk % 4) * 32) >> 4;
+          tc::mma_f16_ss(tmem_base + x * kBlockN, desc_qx + offset, desc_kj + offset, idesc_s, kk != 0);
         }
         tc::mma_commit(&bars->s_full[x]);
-      };
-      // O_x += P_x(j) . V_j; P is read from the first 64 (packed) score columns of tile x
-      // O_x += P_x(j) . V_j in two halves of 64 keys, each as soon as its part of P is in TMEM.
-      // Key block kk (16 keys, 8 packed columns) was written by column half (kk%4)/2 of the softmax
-      // warps into its own score columns: (kk/4)*64 + ((kk%4)/2)*32 + (kk%2)*8.
-      auto issue_values = [&](int x, int j) -> bool {
-        const uint32_t v_address = ring_address + RingPosition(2 * j + 1).slot * kTileBytes;
+      }
+    };
+    // O_x += P_x(j) . V_j in two halves of 64 keys, each as soon as its part of P is in TMEM.  Key block kk
+    // (16 keys, 8 packed columns) was written by column half (kk%4)/2 of the softmax warps into its own
+    // score columns: (kk/4)*64 + ((kk%4)/2)*32 + (kk%2)*8.
+    auto issue_values = [&](int x, int j) -> bool {
+      const uint64_t desc_vj = desc_v + ((RingPosition(2 * j + 1).slot * kTileBytes) >> 4);
+      const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          if (!tc::mbar_wait(&bars->p_ready[x][part], j & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) return false;
-          tc::tc_fence_after_sync();
+      for (int part = 0; part < 2; ++part) {
+        if (!tc::mbar_wait(&bars->p_ready[x][part], j & 1, abort_flag, status, tc::kSiteMmaTmemEmpty)) return false;
+        tc::tc_fence_after_sync();
+        if (issuer) {
 #pragma unroll
           for (int kk = part * 4; kk < part * 4 + 4; ++kk) {
             const uint32_t p_column = (kk / 4) * 64 + ((kk % 4) / 2) * 32 + (kk % 2) * 8;
             // B: 16 key rows = 2048 bytes further down the V tile
-            tc::mma_f16_ts(tmem_base + 2 * kBlockN + x * kMaxHeadDim, tmem_base + x * kBlockN + p_column,
-                           tc::smem_desc_mn_major_sw128(v_address + kk * 2048, kHalfBytes), idesc_o, (j | kk) != 0);
+            tc::mma_f16_ts(tmem_o, tmem_s + p_column, desc_vj + ((kk * 2048) >> 4), idesc_o, (j | kk) != 0);
           }
-        }
-        if (j == tiles_of[x] - 1) tc::mma_commit(&bars->o_full[x]);
-        return true;
-      };
-      auto wait_slot = [&](int index) {
-        const RingPosition at(index);
-        const bool ok = tc::mbar_wait(&bars->slot_full[at.slot], at.phase, abort_flag, status, tc::kSiteMmaFull);
-        tc::tc_fence_after_sync();
-        return ok;
-      };
-      auto release_slot = [&](int index) { tc::mma_commit(&bars->slot_empty[RingPosition(index).slot]); };
-
-      // Tile A's chain P_A(j) -> P.V_A(j) -> S_A(j+1) is the critical one: K_(j+1) and V_j are waited for
-      // while softmax A(j) still runs, so that S_A(j+1) is queued right behind P.V_A(j).
-      alive = alive && wait_slot(0);                                    // K_0
-      for (int j = 0; alive && j < key_tiles; ++j) {
-        if (j < tiles_of[0]) issue_scores(0, j);
-        if (j >= 1) {                                                   // P.V_B(j-1): covers softmax A(j)
-          if (!wait_slot(2 * j - 1) || !issue_values(1, j - 1)) { alive = false; break; }
-          release_slot(2 * j - 1);                                      // V_(j-1): both tiles are done with it
-        }
-        issue_scores(1, j);                                             // tile B sees every key tile
-        release_slot(2 * j);                                            // K_j
-        if (j + 1 < key_tiles && !wait_slot(2 * j + 2)) { alive = false; break; }   // K_(j+1)
-        if (j < tiles_of[0]) {                                          // P.V_A(j): covers softmax B(j)
-          if (!wait_slot(2 * j + 1) || !issue_values(0, j)) { alive = false; break; }
+          if (part == 1 && j == tiles_of[x] - 1) tc::mma_commit(&bars->o_full[x]);
         }
       }
-      if (alive && wait_slot(2 * key_tiles - 1) && issue_values(1, key_tiles - 1)) release_slot(2 * key_tiles - 1);
+      return true;
+    };
+
+    // Tile A's chain P_A(j) -> P.V_A(j) -> S_A(j+1) is the critical one: K_(j+1) and V_j are waited for
+    // while softmax A(j) still runs, so that S_A(j+1) is queued right behind P.V_A(j).
+    bool alive = tc::mbar_wait(&bars->q_full, 0, abort_flag, status, tc::kSiteMmaFull) && wait_slot(0);   // Q, K_0
+    for (int j = 0; alive && j < key_tiles; ++j) {
+      if (j < tiles_of[0]) issue_scores(0, j);
+      if (j >= 1) {                                                   // P.V_B(j-1): covers softmax A(j)
+        if (!wait_slot(2 * j - 1) || !issue_values(1, j - 1)) { alive = false; break; }
+        release_slot(2 * j - 1);                                      // V_(j-1): both tiles are done with it
+      }
+      issue_scores(1, j);                                             // tile B sees every key tile
+      release_slot(2 * j);                                            // K_j
+      if (j + 1 < key_tiles && !wait_slot(2 * j + 2)) { alive = false; break; }   // K_(j+1)
+      if (j < tiles_of[0]) {                                          // P.V_A(j): covers softmax B(j)
+        if (!wait_slot(2 * j + 1) || !issue_values(0, j)) { alive = false; break; }
+      }
     }
+    if (alive && wait_slot(2 * key_tiles - 1) && issue_values(1, key_tiles - 1)) release_slot(2 * key_tiles - 1);
   } else {
     // -------------------------------------------------------------- softmax
-    const int x = (warp - 2) >> 3;                // 0: tile A (warps 2..9), 1: tile B (warps 10..17)
-    const int half = ((warp - 2) >> 2) & 1;       // which 64 of the 128 score columns this thread owns
+    const int x = (warp - kFirstSoftmaxWarp) >> 3;             // 0: tile A, 1: tile B
+    const int half = ((warp - kFirstSoftmaxWarp) >> 2) & 1;    // which 64 of the 128 score columns this thread owns
     const int quadrant = warp & 3;                // TMEM lanes [32*quadrant, +32) are this warp's
     const int row_in_tile = quadrant * 32 + lane;
     const int pair_barrier = 1 + x * 4 + quadrant;  // the two warps that own the same 32 rows
     const int tile_q0 = q0 + x * kBlockM;
     const int q_row = tile_q0 + row_in_tile;
     const int my_tiles = tiles_of[x];
-    constexpr int kColumns = kBlockN / 2;         // scores per thread and step
     constexpr int kOutColumns = kHeadDim / 2;     // output columns per thread
     const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
     const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
@@ -281,36 +301,41 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t phase = j & 1;
       if (!tc::mbar_wait(&bars->s_full[x], phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
       tc::tc_fence_after_sync();
-      // Two passes over this thread's scores (TMEM reads are cheap) keep 32 of them in registers at a
-      // time; P only ever goes over columns this thread has already consumed.
+      // Two passes over this thread's 64 scores, 16 at a time (TMEM reads are cheap): the read of the next 16
+      // is in flight while the current 16 are worked on, and the first read of pass 2 is issued before the
+      // two threads of the row meet.  P only ever goes over columns this thread has already consumed.
       const uint32_t my_scores = tmem_s + lane_base + half * 32;   // chunk c: + c * 64
       const int k0 = j * kBlockN + half * 32;                      // first key of chunk 0; chunk 1: + 64
       const bool masked_tile = (j * kBlockN + kBlockN > shape.seq_k) || (shape.causal && j * kBlockN + kBlockN - 1 > tile_q0);
-      // columns of chunk c at or beyond limit - c*64 hold no valid key
+      // score (c, i) holds no valid key when c*64 + i >= limit
       const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
-      float partial_max[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) partial_max[u] = -INFINITY;
-#pragma unroll
-      for (int chunk = 0; chunk < kColumns / 32; ++chunk) {
-        uint32_t raw[32];
-        tc::tmem_load_32x32(my_scores + chunk * 64, raw);
-        tc::tmem_load_wait();
+      auto column_of = [&](int q) { return my_scores + (q >> 1) * 64 + (q & 1) * 16; };   // 16-column group q of 4
+      auto mask = [&](uint32_t (&scores)[16], int q) {
         if (masked_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (chunk * 64 + i >= limit) raw[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < 16; ++i)
+            if ((q >> 1) * 64 + (q & 1) * 16 + i >= limit) scores[i] = 0xff800000u;  // -inf
         }
+      };
+      uint32_t buffer[2][16];
+      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      tc::tmem_load_32x16(column_of(0), buffer[0]);
+      tc::tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) partial_max[i & 7] = fmaxf(partial_max[i & 7], __uint_as_float(raw[i]));
+      for (int q = 0; q < 4; ++q) {
+        tc::tmem_load_32x16(column_of((q + 1) & 3), buffer[(q + 1) & 1]);   // q = 3: group 0 again, for pass 2
+        mask(buffer[q & 1], q);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) partial_max[i & 3] = fmaxf(partial_max[i & 3], __uint_as_float(buffer[q & 1][i]));
+        if (q < 3) tc::tmem_load_wait();
       }
-      float tile_max = fmaxf(fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])),
-                             fmaxf(fmaxf(partial_max[4], partial_max[5]), fmaxf(partial_max[6], partial_max[7])));
+      float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
       bars->exchange[x][phase][half][row_in_tile] = tile_max;
       named_barrier_sync(pair_barrier, 64);
       tile_max = fmaxf(tile_max, bars->exchange[x][phase][half ^ 1][row_in_tile]) * shape.scale_log2;
       // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
       const bool grow = tile_max > reference + kRescaleThreshold;
+      tc::tmem_load_wait();       // group 0 of pass 2 is in buffer[0]
       if (__any_sync(0xffffffffu, grow)) {
         const float factor = grow ? ex2_approx_ftz(reference - tile_max) : 1.0f;  // 0 on the first tile
         if (grow) { reference = tile_max; sum *= factor; }
@@ -330,29 +355,26 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float offset = -reference;
       float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int chunk = 0; chunk < kColumns / 32; ++chunk) {
-        uint32_t raw[32];
-        tc::tmem_load_32x32(my_scores + chunk * 64, raw);
-        tc::tmem_load_wait();
-        if (masked_tile) {
+      for (int q = 0; q < 4; ++q) {
+        if (q < 3) tc::tmem_load_32x16(column_of(q + 1), buffer[(q + 1) & 1]);
+        mask(buffer[q & 1], q);
+        uint32_t packed[8];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (chunk * 64 + i >= limit) raw[i] = 0xff800000u;
-        }
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(raw[2 * i]), shape.scale_log2, offset));
-          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(raw[2 * i + 1]), shape.scale_log2, offset));
+        for (int i = 0; i < 8; ++i) {
+          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i]), shape.scale_log2, offset));
+          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i + 1]), shape.scale_log2, offset));
           partial_sum[(2 * i) & 3] += p0;
           partial_sum[(2 * i + 1) & 3] += p1;
           packed[i] = pack_pair<T>(p0, p1);
         }
-        tc::tmem_store_32x16(my_scores + chunk * 64, packed);
-        tc::tmem_store_wait();
-        tc::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&bars->p_ready[x][chunk]);
+        tc::tmem_store_32x8(my_scores + (q >> 1) * 64 + (q & 1) * 8, packed);
+        if (q & 1) {           // 64 keys of P are complete
+          tc::tmem_store_wait();
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bars->p_ready[x][q >> 1]);
+        }
+        if (q < 3) tc::tmem_load_wait();
       }
       sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
     }
@@ -444,14 +466,14 @@ int attention_typed(const T *q, const T *k, const T *v, T *o, const int64_t *qd,
   if (result != B200_OK) return result;
   result = tensor_map_4d(&map_v, v, batch, heads_k, seq_k, kHeadDim, vs[0], vs[1], vs[2]);
   if (result != B200_OK) return result;
-  auto kernel = attention_kernel<T, kHeadDim>;
-  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, kSmemBytes));
   Shape shape;
   shape.batch = (int)batch; shape.heads_q = (int)heads_q; shape.seq_q = (int)seq_q; shape.seq_k = (int)seq_k;
   shape.head_group = head_group; shape.causal = causal;
   shape.o_stride_b = os[0]; shape.o_stride_h = os[1]; shape.o_stride_s = os[2];
   shape.scale_log2 = scale * (float)1.4426950408889634;  // scale * LOG2E, rounded to f32 like the kernel definition
   const dim3 grid((unsigned)((seq_q + 2 * kBlockM - 1) / (2 * kBlockM)), (unsigned)heads_q, (unsigned)batch);
+  auto kernel = attention_kernel<T, kHeadDim>;
+  B200_CUDA_TRY(opt_in_dynamic_smem(kernel, kSmemBytes));
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, o, shape, status);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
