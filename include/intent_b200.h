@@ -261,6 +261,14 @@ int b200_gemm_static_scratch(const void *a, int64_t a_d0, int64_t a_d1, int64_t 
  * (lib/Target/NVIDIA/IR/Target.cpp:62-86).  Requires unit innermost strides,
  * D == DV in {64, 128}, other strides positive multiples of 8 elements, 16-byte
  * aligned bases and scale > 0.  An empty key sequence yields zeros.
+ * Numerics, where they differ from the reference's fold (which rescales at every
+ * key chunk): the running maximum m a row's exponentials are taken against is only
+ * replaced -- and O and the row sum rescaled by exp2(m_old - m_new) -- when a key
+ * tile's maximum exceeds m by more than 8 (log2 units, i.e. 2^8).  Between rescales
+ * p = exp2(s*scale*log2e - m) can reach 2^8, well inside f16/bf16/f32 range; P is
+ * rounded to the operand type before P.V and the row sum is accumulated in f32 from
+ * the unrounded p.  The result equals the reference's up to rounding; the parity
+ * tests allow 1e-2 relative.
  */
 int b200_flash_attention(const void *q, int64_t q_d0, int64_t q_d1, int64_t q_d2, int64_t q_d3,
                          int64_t q_s0, int64_t q_s1, int64_t q_s2, int64_t q_s3,
