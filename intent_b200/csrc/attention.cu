@@ -46,7 +46,6 @@
 // stops one key tile before tile B); the diagonal tile and the ragged last key
 // tile are masked element-wise.
 // Work per launch: 4*B*H*D*S*(S+1)/2 flop (causal), 4*B*H*S*D*2 compulsory bytes.
-#include <mutex>
 #include <type_traits>
 
 #include "tc.cuh"
