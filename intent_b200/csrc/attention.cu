@@ -70,6 +70,7 @@ struct __align__(8) Barriers {
   uint64_t s_full[2], p_ready[2][2], o_full[2];   // p_ready: [tile][64-key half of the step]
   uint32_t tmem_base;
   int abort_flag;
+  int softmax_abort[2][4];            // [tile][quadrant]: one of the two warps of these rows gave up
   // the two threads that share a query row (one per column half) exchange their maxima and sums here
   float exchange[2][2][2][kBlockM];   // maxima: [tile][step parity][column half][row]
   float sums[2][2][kBlockM];          // [tile][column half][row]
@@ -115,6 +116,170 @@ struct RingPosition {
   __device__ explicit RingPosition(int index) : slot(index % kRingSlots), phase((index / kRingSlots) & 1) {}
 };
 
+// What the softmax warps of one query tile need: its barriers, exchange space and TMEM columns.
+struct SoftmaxTile {
+  uint64_t *s_full, *o_full, *p_ready;   // p_ready: the two 64-key halves of a step
+  float (*exchange)[2][kBlockM];         // maxima: [step parity][column half][row]
+  float (*sums)[kBlockM];                // [column half][row]
+  int *gave_up;                          // of the two warps that own this thread's rows
+  uint32_t tmem_s, tmem_o;
+  int q0, key_tiles;                     // first query row of the tile, key tiles it walks
+  int first_barrier;                     // named barriers first_barrier .. +3, one per quadrant
+};
+
+// How the softmax warps wait and arrive: bounded waits that report through the caller's workspace.
+struct CtaSync {
+  volatile int *abort_flag;
+  int *status;
+  __device__ bool wait(uint64_t *bar, uint32_t parity, int site) const {
+    return tc::mbar_wait(bar, parity, abort_flag, status, site);
+  }
+  __device__ void arrive(uint64_t *bar) const { tc::mbar_arrive(bar); }
+};
+
+// The softmax of one thread's half row over all key tiles, then its half of the output row.  Two threads
+// share a query row (`half` 0 / 1 owns score columns [32h, 32h+32) and [64+32h, 64+32h+32)); `quadrant`
+// is the warp's TMEM lane quadrant.
+template <typename T, int kHeadDim>
+__device__ __forceinline__ void softmax_rows(const SoftmaxTile &tile, const CtaSync &sync, const Shape &shape,
+                                             T *__restrict__ out, int head, int batch, int half, int quadrant,
+                                             int lane) {
+  const int row_in_tile = quadrant * 32 + lane;
+  const int pair_barrier = tile.first_barrier + quadrant;   // the two warps that own the same 32 rows
+  const int q_row = tile.q0 + row_in_tile;
+  constexpr int kOutColumns = kHeadDim / 2;     // output columns per thread
+  const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+  float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
+  float sum = 0.0f;             // of this thread's columns only; the halves are added at the end
+  bool alive = true;
+  for (int j = 0; j < tile.key_tiles; ++j) {
+    const uint32_t phase = j & 1;
+    // The two warps of a row meet at a named barrier below, so they must leave together: a warp whose
+    // wait gave up says so in shared memory and both decide after the barrier.
+    const bool ready = sync.wait(tile.s_full, phase, tc::kSiteSoftmax);
+    if (!ready) *tile.gave_up = 1;
+    tc::tc_fence_after_sync();
+    // Two passes over this thread's 64 scores, 16 at a time (TMEM reads are cheap): the read of the next 16
+    // is in flight while the current 16 are worked on, and the first read of pass 2 is issued before the
+    // two threads of the row meet.  P only ever goes over columns this thread has already consumed.
+    const uint32_t my_scores = tile.tmem_s + lane_base + half * 32;   // chunk c: + c * 64
+    const int k0 = j * kBlockN + half * 32;                      // first key of chunk 0; chunk 1: + 64
+    const bool masked_tile = (j * kBlockN + kBlockN > shape.seq_k) || (shape.causal && j * kBlockN + kBlockN - 1 > tile.q0);
+    // score (c, i) holds no valid key when c*64 + i >= limit
+    const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
+    auto column_of = [&](int q) { return my_scores + (q >> 1) * 64 + (q & 1) * 16; };   // 16-column group q of 4
+    auto mask = [&](uint32_t (&scores)[16], int q) {
+      if (masked_tile) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if ((q >> 1) * 64 + (q & 1) * 16 + i >= limit) scores[i] = 0xff800000u;  // -inf
+      }
+    };
+    uint32_t buffer[2][16];
+    float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    if (ready) {
+      tc::tmem_load_32x16(column_of(0), buffer[0]);
+      tc::tmem_load_wait();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        tc::tmem_load_32x16(column_of((q + 1) & 3), buffer[(q + 1) & 1]);   // q = 3: group 0 again, for pass 2
+        mask(buffer[q & 1], q);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) partial_max[i & 3] = fmaxf(partial_max[i & 3], __uint_as_float(buffer[q & 1][i]));
+        if (q < 3) tc::tmem_load_wait();
+      }
+    }
+    float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
+    tile.exchange[phase][half][row_in_tile] = tile_max;
+    named_barrier_sync(pair_barrier, 64);
+    if (*reinterpret_cast<volatile int *>(tile.gave_up)) {
+      tc::tmem_load_wait();
+      alive = false;
+      break;
+    }
+    tile_max = fmaxf(tile_max, tile.exchange[phase][half ^ 1][row_in_tile]) * shape.scale_log2;
+    // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
+    const bool grow = tile_max > reference + kRescaleThreshold;
+    tc::tmem_load_wait();       // group 0 of pass 2 is in buffer[0]
+    if (__any_sync(0xffffffffu, grow)) {
+      const float factor = grow ? ex2_approx_ftz(reference - tile_max) : 1.0f;  // 0 on the first tile
+      if (grow) { reference = tile_max; sum *= factor; }
+      if (j > 0) {
+        // S(j) has completed, hence this tile's P.V(j-1) too: O is quiescent until p_ready is signalled
+#pragma unroll 1
+        for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
+          uint32_t raw[32];
+          tc::tmem_load_32x32(tile.tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
+          tc::tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * factor);
+          tc::tmem_store_32x32(tile.tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
+        }
+      }
+    }
+    const float offset = -reference;
+    float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (q < 3) tc::tmem_load_32x16(column_of(q + 1), buffer[(q + 1) & 1]);
+      mask(buffer[q & 1], q);
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i]), shape.scale_log2, offset));
+        const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i + 1]), shape.scale_log2, offset));
+        partial_sum[(2 * i) & 3] += p0;
+        partial_sum[(2 * i + 1) & 3] += p1;
+        packed[i] = pack_pair<T>(p0, p1);
+      }
+      tc::tmem_store_32x8(my_scores + (q >> 1) * 64 + (q & 1) * 8, packed);
+      if (q & 1) {           // 64 keys of P are complete
+        tc::tmem_store_wait();
+        tc::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) sync.arrive(tile.p_ready + (q >> 1));
+      }
+      if (q < 3) tc::tmem_load_wait();
+    }
+    sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
+  }
+  // the row sum is the sum of both halves (they share the reference maximum)
+  tile.sums[half][row_in_tile] = sum;
+  named_barrier_sync(pair_barrier, 64);
+  sum += tile.sums[half ^ 1][row_in_tile];
+  if (alive && sync.wait(tile.o_full, 0, tc::kSiteEpilogueTmemFull)) {
+    tc::tc_fence_after_sync();
+    const float inverse = div_approx_ftz(1.0f, sum);
+    T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s +
+                     half * kOutColumns;
+    const bool vector_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && shape.o_stride_b % 8 == 0 &&
+                           shape.o_stride_h % 8 == 0 && shape.o_stride_s % 8 == 0;
+#pragma unroll 1
+    for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
+      uint32_t raw[32];
+      tc::tmem_load_32x32(tile.tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
+      tc::tmem_load_wait();
+      if (q_row < shape.seq_q) {
+        if (vector_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            v.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]) * inverse, __uint_as_float(raw[q * 8 + 1]) * inverse);
+            v.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]) * inverse, __uint_as_float(raw[q * 8 + 3]) * inverse);
+            v.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]) * inverse, __uint_as_float(raw[q * 8 + 5]) * inverse);
+            v.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]) * inverse, __uint_as_float(raw[q * 8 + 7]) * inverse);
+            *reinterpret_cast<uint4 *>(destination + chunk * 32 + q * 8) = v;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            destination[chunk * 32 + i] = Element<T>::narrow(__uint_as_float(raw[i]) * inverse);
+        }
+      }
+    }
+  }
+}
+
 template <typename T, int kHeadDim>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -156,6 +321,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc::mbar_init(&bars->o_full[x], 1);
     }
     bars->abort_flag = 0;
+    for (int i = 0; i < 8; ++i) (&bars->softmax_abort[0][0])[i] = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_descriptor(&map_q);
     tc::tma_prefetch_descriptor(&map_k);
@@ -283,135 +449,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   } else {
     // -------------------------------------------------------------- softmax
     const int x = (warp - kFirstSoftmaxWarp) >> 3;             // 0: tile A, 1: tile B
-    const int half = ((warp - kFirstSoftmaxWarp) >> 2) & 1;    // which 64 of the 128 score columns this thread owns
-    const int quadrant = warp & 3;                // TMEM lanes [32*quadrant, +32) are this warp's
-    const int row_in_tile = quadrant * 32 + lane;
-    const int pair_barrier = 1 + x * 4 + quadrant;  // the two warps that own the same 32 rows
-    const int tile_q0 = q0 + x * kBlockM;
-    const int q_row = tile_q0 + row_in_tile;
-    const int my_tiles = tiles_of[x];
-    constexpr int kOutColumns = kHeadDim / 2;     // output columns per thread
-    const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
-    const uint32_t tmem_s = tmem_base + x * kBlockN, tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
-    float reference = -INFINITY;  // maximum the exponentials are taken against (scaled log2 units)
-    float sum = 0.0f;             // of this thread's columns only; the halves are added at the end
-    bool alive = true;
-    for (int j = 0; alive && j < my_tiles; ++j) {
-      const uint32_t phase = j & 1;
-      if (!tc::mbar_wait(&bars->s_full[x], phase, abort_flag, status, tc::kSiteSoftmax)) { alive = false; break; }
-      tc::tc_fence_after_sync();
-      // Two passes over this thread's 64 scores, 16 at a time (TMEM reads are cheap): the read of the next 16
-      // is in flight while the current 16 are worked on, and the first read of pass 2 is issued before the
-      // two threads of the row meet.  P only ever goes over columns this thread has already consumed.
-      const uint32_t my_scores = tmem_s + lane_base + half * 32;   // chunk c: + c * 64
-      const int k0 = j * kBlockN + half * 32;                      // first key of chunk 0; chunk 1: + 64
-      const bool masked_tile = (j * kBlockN + kBlockN > shape.seq_k) || (shape.causal && j * kBlockN + kBlockN - 1 > tile_q0);
-      // score (c, i) holds no valid key when c*64 + i >= limit
-      const int limit = shape.causal ? min(shape.seq_k - k0, q_row - k0 + 1) : shape.seq_k - k0;
-      auto column_of = [&](int q) { return my_scores + (q >> 1) * 64 + (q & 1) * 16; };   // 16-column group q of 4
-      auto mask = [&](uint32_t (&scores)[16], int q) {
-        if (masked_tile) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if ((q >> 1) * 64 + (q & 1) * 16 + i >= limit) scores[i] = 0xff800000u;  // -inf
-        }
-      };
-      uint32_t buffer[2][16];
-      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      tc::tmem_load_32x16(column_of(0), buffer[0]);
-      tc::tmem_load_wait();
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        tc::tmem_load_32x16(column_of((q + 1) & 3), buffer[(q + 1) & 1]);   // q = 3: group 0 again, for pass 2
-        mask(buffer[q & 1], q);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) partial_max[i & 3] = fmaxf(partial_max[i & 3], __uint_as_float(buffer[q & 1][i]));
-        if (q < 3) tc::tmem_load_wait();
-      }
-      float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
-      bars->exchange[x][phase][half][row_in_tile] = tile_max;
-      named_barrier_sync(pair_barrier, 64);
-      tile_max = fmaxf(tile_max, bars->exchange[x][phase][half ^ 1][row_in_tile]) * shape.scale_log2;
-      // A row of the first key tile always holds key 0, so `reference` is finite from j = 0 on.
-      const bool grow = tile_max > reference + kRescaleThreshold;
-      tc::tmem_load_wait();       // group 0 of pass 2 is in buffer[0]
-      if (__any_sync(0xffffffffu, grow)) {
-        const float factor = grow ? ex2_approx_ftz(reference - tile_max) : 1.0f;  // 0 on the first tile
-        if (grow) { reference = tile_max; sum *= factor; }
-        if (j > 0) {
-          // S(j) has completed, hence this tile's P.V(j-1) too: O is quiescent until p_ready is signalled
-#pragma unroll 1
-          for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
-            uint32_t raw[32];
-            tc::tmem_load_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
-            tc::tmem_load_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * factor);
-            tc::tmem_store_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
-          }
-        }
-      }
-      const float offset = -reference;
-      float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        if (q < 3) tc::tmem_load_32x16(column_of(q + 1), buffer[(q + 1) & 1]);
-        mask(buffer[q & 1], q);
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i]), shape.scale_log2, offset));
-          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(buffer[q & 1][2 * i + 1]), shape.scale_log2, offset));
-          partial_sum[(2 * i) & 3] += p0;
-          partial_sum[(2 * i + 1) & 3] += p1;
-          packed[i] = pack_pair<T>(p0, p1);
-        }
-        tc::tmem_store_32x8(my_scores + (q >> 1) * 64 + (q & 1) * 8, packed);
-        if (q & 1) {           // 64 keys of P are complete
-          tc::tmem_store_wait();
-          tc::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive(&bars->p_ready[x][q >> 1]);
-        }
-        if (q < 3) tc::tmem_load_wait();
-      }
-      sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
-    }
-    // the row sum is the sum of both halves (they share the reference maximum)
-    bars->sums[x][half][row_in_tile] = sum;
-    named_barrier_sync(pair_barrier, 64);
-    sum += bars->sums[x][half ^ 1][row_in_tile];
-    if (alive && tc::mbar_wait(&bars->o_full[x], 0, abort_flag, status, tc::kSiteEpilogueTmemFull)) {
-      tc::tc_fence_after_sync();
-      const float inverse = div_approx_ftz(1.0f, sum);
-      T *destination = out + batch * shape.o_stride_b + head * shape.o_stride_h + (int64_t)q_row * shape.o_stride_s +
-                       half * kOutColumns;
-      const bool vector_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && shape.o_stride_b % 8 == 0 &&
-                             shape.o_stride_h % 8 == 0 && shape.o_stride_s % 8 == 0;
-#pragma unroll 1
-      for (int chunk = 0; chunk < kOutColumns / 32; ++chunk) {
-        uint32_t raw[32];
-        tc::tmem_load_32x32(tmem_o + lane_base + half * kOutColumns + chunk * 32, raw);
-        tc::tmem_load_wait();
-        if (q_row < shape.seq_q) {
-          if (vector_ok) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 v;
-              v.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]) * inverse, __uint_as_float(raw[q * 8 + 1]) * inverse);
-              v.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]) * inverse, __uint_as_float(raw[q * 8 + 3]) * inverse);
-              v.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]) * inverse, __uint_as_float(raw[q * 8 + 5]) * inverse);
-              v.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]) * inverse, __uint_as_float(raw[q * 8 + 7]) * inverse);
-              *reinterpret_cast<uint4 *>(destination + chunk * 32 + q * 8) = v;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              destination[chunk * 32 + i] = Element<T>::narrow(__uint_as_float(raw[i]) * inverse);
-          }
-        }
-      }
-    }
+    SoftmaxTile tile;
+    tile.s_full = &bars->s_full[x]; tile.o_full = &bars->o_full[x]; tile.p_ready = bars->p_ready[x];
+    tile.exchange = bars->exchange[x]; tile.sums = bars->sums[x]; tile.gave_up = &bars->softmax_abort[x][warp & 3];
+    tile.tmem_s = tmem_base + x * kBlockN; tile.tmem_o = tmem_base + 2 * kBlockN + x * kMaxHeadDim;
+    tile.q0 = q0 + x * kBlockM; tile.key_tiles = tiles_of[x]; tile.first_barrier = 1 + x * 4;
+    softmax_rows<T, kHeadDim>(tile, CtaSync{abort_flag, status}, shape, out, head, batch,
+                              ((warp - kFirstSoftmaxWarp) >> 2) & 1, warp & 3, lane);
   }
 
   tc::tc_fence_before_sync();
