@@ -182,33 +182,41 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- MMA issuer
-    if (tc::elect_one() && steps > 0) {
+    // The whole warp walks the loop (waits and descriptor arithmetic stay warp-uniform, descriptors are
+    // built once and advanced by byte offsets / 16); one elected lane issues a whole product per branch.
+    if (steps > 0) {
+      const bool issuer = tc::elect_one();
       constexpr int format = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_t = tc::instr_desc_f16(format, kTile, kTile, false);
       constexpr uint32_t idesc_acc = tc::instr_desc_f16(format, kTile, kHeadDim, true);
-      const uint32_t x_address = tc::smem_u32(x_tiles), ring_address = tc::smem_u32(ring);
+      const uint64_t desc_x = tc::smem_desc_k_major_sw128(tc::smem_u32(x_tiles));
+      const uint64_t desc_y = tc::smem_desc_k_major_sw128(tc::smem_u32(ring));
+      const uint64_t desc_y_mn = tc::smem_desc_mn_major_sw128(tc::smem_u32(ring), L::kHalfBytes);
       bool alive = tc::mbar_wait(&bars->x_full, 0, abort_flag, status, tc::kSiteMmaFull);
       tc::tc_fence_after_sync();
       // T0 = X0 . Y0^T or T1 = X1 . Y1^T of one step
       auto issue_scores = [&](int which, int step) {
-        const uint32_t y_address = ring_address + (step % kStages) * 2 * L::kTileBytes;
+        const uint64_t desc_ys = desc_y + (((step % kStages) * 2 * L::kTileBytes) >> 4);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-          const uint32_t offset = which * L::kTileBytes + (kk / 4) * L::kHalfBytes + (kk % 4) * 32;
-          tc::mma_f16_ss(which ? tmem_t1 : tmem_t0, tc::smem_desc_k_major_sw128(x_address + offset),
-                         tc::smem_desc_k_major_sw128(y_address + offset), idesc_t, kk != 0);
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t offset = (which * L::kTileBytes + (kk / 4) * L::kHalfBytes + (kk % 4) * 32) >> 4;
+            tc::mma_f16_ss(which ? tmem_t1 : tmem_t0, desc_x + offset, desc_ys + offset, idesc_t, kk != 0);
+          }
+          tc::mma_commit(which ? &bars->t1_full : &bars->t0_full);
         }
-        tc::mma_commit(which ? &bars->t1_full : &bars->t0_full);
       };
       // acc += (P or G, 16 bits, in TMEM) . (Y1 or Y0 of the step, as an MN-major B operand)
       auto issue_gradient = [&](uint32_t accumulator, uint32_t operand, int which_y, int step) {
-        const uint32_t y_address = ring_address + (step % kStages) * 2 * L::kTileBytes + which_y * L::kTileBytes;
+        const uint64_t desc_ys = desc_y_mn + ((((step % kStages) * 2 + which_y) * L::kTileBytes) >> 4);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          // key block kk (16 streamed rows, 8 packed columns) was written by column half kk/4 into its own
-          // columns; B: the same 16 rows of Y, 2048 bytes apart
-          tc::mma_f16_ts(accumulator, operand + (kk / 4) * 64 + (kk % 4) * 8,
-                         tc::smem_desc_mn_major_sw128(y_address + kk * 2048, L::kHalfBytes), idesc_acc, (step | kk) != 0);
+          for (int kk = 0; kk < kTile / 16; ++kk) {
+            // key block kk (16 streamed rows, 8 packed columns) was written by column half kk/4 into its own
+            // columns; B: the same 16 rows of Y, 2048 bytes apart
+            tc::mma_f16_ts(accumulator, operand + (kk / 4) * 64 + (kk % 4) * 8, desc_ys + ((kk * 2048) >> 4), idesc_acc,
+                           (step | kk) != 0);
+          }
         }
       };
       auto wait_stage = [&](int step) {
@@ -244,7 +252,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
             } else if (!gradient_issued && tc::mbar_try_wait(&bars->g_ready, step & 1)) {
               tc::tc_fence_after_sync();
               issue_gradient(tmem_acc1, tmem_t1, 0, step);
-              tc::mma_commit(&bars->y_empty[step % kStages]);  // both gradient products of the step have read its tiles
+              if (issuer) tc::mma_commit(&bars->y_empty[step % kStages]);  // both gradient products of the step have read its tiles
               gradient_issued = true;
             } else if ((++spins & 0x3ffu) == 0) {
               if (*abort_flag) break;
@@ -258,7 +266,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_x0, const __gr
           }
           if (!(scores_issued && gradient_issued)) break;
           if (more) issue_scores(1, step + 1);
-          else tc::mma_commit(&bars->acc_full);
+          else if (issuer) tc::mma_commit(&bars->acc_full);
         }
       }
     }
