@@ -435,7 +435,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     for (int j = 0; alive && j < key_tiles; ++j) {
       if (j < tiles_of[0]) issue_scores(0, j);
       if (j >= 1) {                                                   // P.V_B(j-1): covers softmax A(j)
-        if (!wait_slot(2 * j - 1) || !issue_values(1, j - 1)) { alive = false; break; }
+        // V_(j-1) was already waited for before P.V_A(j-1) unless tile A had stopped by then
+        if ((j - 1 >= tiles_of[0] && !wait_slot(2 * j - 1)) || !issue_values(1, j - 1)) { alive = false; break; }
         release_slot(2 * j - 1);                                      // V_(j-1): both tiles are done with it
       }
       issue_scores(1, j);                                             // tile B sees every key tile
@@ -445,7 +446,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!wait_slot(2 * j + 1) || !issue_values(0, j)) { alive = false; break; }
       }
     }
-    if (alive && wait_slot(2 * key_tiles - 1) && issue_values(1, key_tiles - 1)) release_slot(2 * key_tiles - 1);
+    if (alive && (key_tiles - 1 < tiles_of[0] || wait_slot(2 * key_tiles - 1)) && issue_values(1, key_tiles - 1))
+      release_slot(2 * key_tiles - 1);
   } else {
     // -------------------------------------------------------------- softmax
     const int x = (warp - kFirstSoftmaxWarp) >> 3;             // 0: tile A, 1: tile B
