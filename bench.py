@@ -836,8 +836,8 @@ def gather_ceiling(case, result: dict) -> dict:
             "one_pass_ms_at_all_of_x_rate": one_pass_ms, "spmm_over_one_pass": result["ms_per_step"] / one_pass_ms,
             "note": "floor = the call's nnz x 512 B of row gathers at the probe's L2-resident rate (what column "
                     "blocks that stay in L2 could reach with free Y traffic); one_pass = the same volume at the "
-                    "rate a single pass over all of X reaches (X is 134 MB; a gathered line is cached by the L2 "
-                    "half next to the SM that asked, so about 60 MB of distinct X stay resident)"}
+                    "rate a single pass over all of X reaches (X is 134 MB; about 60 MB of randomly gathered data "
+                    "is what the 126 MB L2 serves at its full rate)"}
 
 
 OUTPUT_BYTES = {"softmax": 4096 * 1024 * 4, "layer_norm": 16384 * 4096 * 2, "gemm": 8192 * 8192 * 2,
