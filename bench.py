@@ -52,10 +52,10 @@ NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/.
 NCU_TRAFFIC_BYTES = {"softmax": 32286000,      # steady state over rotating operand sets (mean of nine launches)
-                     "layer_norm": 217463040, "gemm": 1222019160, "attention": 1057636608,
+                     "layer_norm": 217463040, "gemm": 1222019160, "attention": 1059586816,
                      "spmm": 983705088, "softmax_backward": 160885760, "spmv": 8672256,
                      # steps of several kernels: the sum over the step's launches
-                     "layer_norm_backward": 74406912 + 2109440, "attention_backward": 274570496 + 847716352}
+                     "layer_norm_backward": 74406912 + 2109440, "attention_backward": 274570496 + 846483200}
 
 
 def peaks() -> tuple[dict, str]:
